@@ -1,0 +1,100 @@
+// 64-bit modular arithmetic for RNS limbs, device side.
+//
+// All moduli are NTT-friendly primes below 2^61, so that 4q fits a signed
+// 64-bit word and lazy (Harvey) butterflies can keep values in [0, 4q).
+// Residues that leave a kernel are always canonical, in [0, q): that is the
+// only property the CPU runtime's results depend on
+// (fhe-cmplr/rtlib/ant/include/util/modular.h:126-256 reduces after every
+// operation), so any reduction that yields the canonical representative of the
+// same integer reproduces it bit for bit.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace fhert {
+
+typedef unsigned long long u64;
+
+// Per-prime constants kept in device memory (one entry per Q or P prime).
+struct DevModulus {
+  u64      q;        // modulus
+  u64      mu_hi;    // floor(2^128 / q), high and low words
+  u64      mu_lo;
+  u64      bar;      // floor(2^(bits-1+64) / q), single-word Barrett constant
+  uint32_t bits;     // bit length of q
+  uint32_t pad;
+  u64      n_inv;    // N^-1 mod q and its Shoup companion
+  u64      n_inv_p;
+};
+
+__device__ __forceinline__ u64 add_mod(u64 a, u64 b, u64 q) {
+  u64 s = a + b;
+  return s >= q ? s - q : s;
+}
+
+__device__ __forceinline__ u64 sub_mod(u64 a, u64 b, u64 q) {
+  return a >= b ? a - b : a + q - b;
+}
+
+// Shoup multiplication by a constant w with companion wp = floor(w*2^64/q).
+// Valid for any 64-bit a; result in [0, 2q).
+__device__ __forceinline__ u64 mul_shoup_lazy(u64 a, u64 w, u64 wp, u64 q) {
+  u64 hi = __umul64hi(a, wp);
+  return a * w - hi * q;
+}
+
+// As above, result canonical in [0, q)  (modular.h:249-256).
+__device__ __forceinline__ u64 mul_shoup(u64 a, u64 w, u64 wp, u64 q) {
+  u64 r = mul_shoup_lazy(a, w, wp, q);
+  return r >= q ? r - q : r;
+}
+
+// Canonical a*b mod q for a, b < 2^61 (product below 2^122).  Single-word
+// Barrett: the quotient estimate is taken from the product shifted right by
+// bits-1, multiplied by bar = floor(2^(bits-1+64)/q); it undershoots the true
+// quotient by at most 2.
+__device__ __forceinline__ u64 mul_mod(u64 a, u64 b, const DevModulus& m) {
+  u64      lo = a * b;
+  u64      hi = __umul64hi(a, b);
+  uint32_t s  = m.bits - 1;
+  u64      x1 = (hi << (64 - s)) | (lo >> s);
+  u64      qh = __umul64hi(x1, m.bar);
+  u64      r  = lo - qh * m.q;
+  if (r >= 2 * m.q) r -= 2 * m.q;
+  if (r >= m.q) r -= m.q;
+  return r;
+}
+
+// Canonical reduction of a 128-bit value (hi:lo) < 2^127 with the two-word
+// constant mu = floor(2^128/q)  (modular.h:185-224 does the same job).  The
+// quotient estimate drops the low partial products and undershoots by at most
+// 3, so the remainder lies in [0, 5q) and 5q < 2^64.
+__device__ __forceinline__ u64 reduce_128(u64 hi, u64 lo, const DevModulus& m) {
+  u64 qh = hi * m.mu_hi + __umul64hi(hi, m.mu_lo) + __umul64hi(lo, m.mu_hi);
+  u64 r  = lo - qh * m.q;
+  if (r >= 4 * m.q) r -= 4 * m.q;
+  if (r >= 2 * m.q) r -= 2 * m.q;
+  if (r >= m.q) r -= m.q;
+  return r;
+}
+
+// acc(hi:lo) += a*b
+__device__ __forceinline__ void mac_128(u64& hi, u64& lo, u64 a, u64 b) {
+  u64 pl = a * b;
+  u64 ph = __umul64hi(a, b);
+  lo += pl;
+  hi += ph + (lo < pl);
+}
+
+// Centred lift of a residue mod q_old into [0, q_new)  (modular.h:296-322):
+// values above floor(q_old/2) stand for negative numbers, so the result is
+// (v mod q_new) or (v - q_old mod q_new).  old_mod_new = q_old mod q_new.
+__device__ __forceinline__ u64 switch_modulus(u64 v, u64 q_old,
+                                              const DevModulus& m_new,
+                                              u64 old_mod_new) {
+  u64 r = reduce_128(0, v, m_new);
+  if (v > (q_old >> 1)) r = sub_mod(r, old_mod_new, m_new.q);
+  return r;
+}
+
+}  // namespace fhert

@@ -1,0 +1,261 @@
+/*
+ * libFHErt_b200 -- CKKS runtime for NVIDIA B200 (sm_100a) behind the C runtime
+ * API that the ANT-ACE FHE compiler emits calls against.
+ *
+ * Every entry point below keeps the name, argument meaning and result of the
+ * CPU runtime function it replaces; the comment on each group cites that
+ * function as <file>:<line> inside fhe-cmplr/rtlib/ of the ANT-ACE tree.
+ *
+ * Data model
+ *   - A polynomial is limb-major: limb i (residues modulo one RNS prime) is the
+ *     N contiguous int64 words at _data + i*N.  Q limbs come first, the K
+ *     special ("P") limbs sit at the end of the allocation
+ *     (ant/poly/include/rns_poly_impl.h:43).  Generated code does pointer
+ *     arithmetic on _data, so this layout is part of the ABI.
+ *   - _data is a DEVICE pointer.  Host code may compute addresses from it but
+ *     must not dereference it; use Fhert_upload / Fhert_download to move
+ *     residues between host buffers and polynomials.
+ *   - All work is queued on one CUDA stream owned by the library
+ *     (Fhert_stream); calls return as soon as their kernels are queued.
+ *     Fhert_download and Fhert_sync wait for completion.
+ *   - Errors: like the CPU runtime (include/common/error.h:17-32) a failed
+ *     precondition prints a message and aborts.  There is no CPU fallback: if
+ *     no CUDA device is usable the first call aborts.
+ */
+#ifndef FHERT_B200_H
+#define FHERT_B200_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------ */
+/* Types (field names are those generated programs touch directly)          */
+/* ------------------------------------------------------------------------ */
+
+/* ant/include/util/modular.h:21-26 */
+typedef struct {
+  int64_t           _val;
+  int64_t           _br_k;
+  int64_t           _br_m;
+  unsigned __int128 _prec128;
+} MODULUS;
+
+/* ant/include/poly/rns_poly.h:23-32 */
+typedef struct {
+  uint32_t _ring_degree;
+  size_t   _num_alloc_primes;
+  size_t   _num_primes;
+  size_t   _num_primes_p;
+  bool     _is_ntt;
+  int64_t* _data; /* device memory */
+} POLYNOMIAL;
+typedef POLYNOMIAL* POLY;
+typedef POLYNOMIAL* POLY_ARR;
+
+/* ant/include/ckks/ciphertext.h:29-35, 260-267; plaintext.h:26-31 */
+typedef struct {
+  POLYNOMIAL _c0_poly;
+  POLYNOMIAL _c1_poly;
+  uint32_t   _slots;
+  double     _scaling_factor;
+  uint32_t   _sf_degree;
+} CIPHERTEXT;
+typedef CIPHERTEXT* CIPHER;
+
+typedef struct {
+  POLYNOMIAL _c0_poly;
+  POLYNOMIAL _c1_poly;
+  POLYNOMIAL _c2_poly;
+  uint32_t   _slots;
+  double     _scaling_factor;
+  uint32_t   _sf_degree;
+} CIPHERTEXT3;
+typedef CIPHERTEXT3* CIPHER3;
+
+typedef struct {
+  POLYNOMIAL _poly;
+  uint32_t   _slots;
+  double     _scaling_factor;
+  uint32_t   _sf_degree;
+} PLAINTEXT;
+typedef PLAINTEXT* PLAIN;
+
+/* ant/include/ckks/public_key.h:24-27, switch_key.h:27-29.  One hybrid
+ * key-switch key: per digit a pair of polynomials over Q u P, NTT form. */
+typedef struct {
+  POLYNOMIAL _p0;
+  POLYNOMIAL _p1;
+} PUBLIC_KEY;
+typedef struct {
+  size_t      _num_parts;
+  PUBLIC_KEY* _parts;
+} SWITCH_KEY;
+typedef SWITCH_KEY* SW_KEY;
+
+/* include/common/common.h:73-85 */
+typedef enum { LIB_ANT = 0 } LIB_PROV;
+typedef struct {
+  LIB_PROV _provider;
+  uint32_t _poly_degree;
+  size_t   _sec_level;
+  size_t   _mul_depth;
+  size_t   _input_level;
+  size_t   _first_mod_size;
+  size_t   _scaling_mod_size;
+  size_t   _num_q_parts;
+  size_t   _hamming_weight;
+  size_t   _num_rot_idx;
+  int32_t  _rot_idxs[];
+} CKKS_PARAMS;
+
+/* ------------------------------------------------------------------------ */
+/* Context  (ant/context/src/ckks_context.c:84-217, ant/util/src/crt.c)      */
+/* ------------------------------------------------------------------------ */
+
+/* Supplied by the compiled program (include/common/rt_api.h:48-80).  The
+ * library carries a weak default that returns what Fhert_set_context_params
+ * stored, so a host without a compiled program (tests, benchmarks) can create
+ * a context too. */
+CKKS_PARAMS* Get_context_params(void);
+void Fhert_set_context_params(uint32_t degree, size_t num_q, size_t q0_bits,
+                              size_t sf_bits, size_t num_q_parts,
+                              size_t input_level, size_t hamming_weight,
+                              size_t num_rot, const int32_t* rot_idxs);
+
+/* Prepare_context builds the prime chain, the NTT and base-conversion tables
+ * (same primes, roots and constants as ckks_context.c:84 -> crt.c:607) and
+ * uploads them.  Keys are generated unless FHERT_SKIP_KEYGEN=1 is set, in
+ * which case they are supplied with Fhert_import_switch_key. */
+void     Prepare_context(void);
+void     Finalize_context(void);
+uint32_t Degree(void);         /* ckks_context.c:163 */
+size_t   Get_q_cnt(void);      /* number of Q primes L */
+size_t   Get_p_cnt(void);      /* number of special primes K */
+size_t   Get_q_parts(void);    /* dnum */
+size_t   Get_part_size(void);  /* alpha = ceil(L/dnum), crt.c:419 */
+MODULUS* Q_modulus(void);      /* head of contiguous MODULUS[L], crt.c:1117 */
+MODULUS* P_modulus(void);      /* head of contiguous MODULUS[K], crt.c:1121 */
+double   Get_default_sc(void); /* 2^sf_bits */
+
+/* primes[0..L) = Q chain, primes[L..L+K) = P chain */
+void Fhert_get_primes(int64_t* primes);
+/* host copy of one prime's forward / inverse twiddles (w, floor(w*2^64/q))
+ * in the bit-reversed order of ant/util/src/ntt.c:91-138 */
+void Fhert_get_ntt_tables(size_t prime_idx, int64_t* rou, uint64_t* rou_prec,
+                          int64_t* rou_inv, uint64_t* rou_inv_prec,
+                          int64_t* degree_inv);
+
+/* ------------------------------------------------------------------------ */
+/* Memory  (ant/include/poly/rns_poly.h:109-268, ant/poly/src/rns_poly.c:1319) */
+/* ------------------------------------------------------------------------ */
+
+POLY Alloc_poly(uint32_t degree, size_t num_q, size_t num_p);
+void Free_poly(POLY poly);
+void Alloc_poly_data(POLY poly, uint32_t degree, size_t num_q, size_t num_p);
+void Free_poly_data(POLY poly);
+void Init_poly_by_size(POLY res, size_t num_q, bool is_ext);
+void Copy_poly(POLY res, POLY poly); /* rns_poly.c:57-72 */
+int64_t* Coeffs(POLY poly, uint32_t limb, uint32_t degree);
+void     Set_coeffs(POLY poly, uint32_t limb, uint32_t degree, int64_t* src);
+
+/* host <-> device: `limbs` consecutive limbs starting at limb `first` of the
+ * allocation (P limbs are addressed by their allocation index) */
+void Fhert_upload(POLY poly, size_t first, size_t limbs, const int64_t* host);
+void Fhert_download(POLY poly, size_t first, size_t limbs, int64_t* host);
+void Fhert_sync(void);
+void* Fhert_stream(void);                /* cudaStream_t of the library */
+uint64_t Fhert_kernel_launches(void);    /* kernels queued since load */
+/* Per-kernel device timing: between begin and end every kernel launch is
+ * bracketed by CUDA events on the library stream; end waits for the stream and
+ * writes one "name launches limbs total_ms" line per kernel into buf (limbs =
+ * limbs covered by those launches). */
+void   Fhert_profile_begin(void);
+size_t Fhert_profile_end(char* buf, size_t cap);
+
+/* ------------------------------------------------------------------------ */
+/* Per-limb vector ops  (ant/hal/src/hal.c:15-153)                           */
+/* ------------------------------------------------------------------------ */
+
+int64_t* Hw_modadd(int64_t* res, int64_t* a, int64_t* b, MODULUS* m, uint32_t degree);
+int64_t* Hw_modsub(int64_t* res, int64_t* a, int64_t* b, MODULUS* m, uint32_t degree);
+int64_t* Hw_modmul(int64_t* res, int64_t* a, int64_t* b, MODULUS* m, uint32_t degree);
+/* res += a * b */
+int64_t* Hw_modmuladd(int64_t* res, int64_t* a, int64_t* b, MODULUS* m, uint32_t degree);
+int64_t* Hw_modadd_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint32_t degree);
+int64_t* Hw_modmul_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint32_t degree);
+/* res[i] = val[order[i]]; `order` is what Auto_order returned */
+int64_t* Hw_rotate(int64_t* res, int64_t* val, int64_t* order, MODULUS* m, uint32_t degree);
+/* negacyclic NTT / inverse NTT of one limb of prime `mod_idx` (0..L+K-1),
+ * natural -> bit-reversed order and back (ant/util/src/ntt.c:140-330) */
+void Hw_ntt(int64_t* res, int64_t* val, size_t mod_idx, uint32_t degree);
+void Hw_intt(int64_t* res, int64_t* val, size_t mod_idx, uint32_t degree);
+
+/* ------------------------------------------------------------------------ */
+/* RNS polynomial ops  (ant/poly/src/rns_poly.c)                             */
+/* ------------------------------------------------------------------------ */
+
+POLY   Conv_poly2ntt_inplace(POLY poly);              /* rns_poly.c:608-699 */
+POLY   Conv_ntt2poly_inplace(POLY poly);
+POLY   Add_poly(POLY res, POLY a, POLY b);            /* rns_poly.c:852 */
+POLY   Sub_poly(POLY res, POLY a, POLY b);            /* rns_poly.c:900 */
+POLY   Mul_poly(POLY res, POLY a, POLY b);            /* rns_poly.c:950 */
+POLY   Rescale(POLY res, POLY poly);                  /* rns_poly.c:310 */
+POLY   Modswitch(POLY res, POLY poly);                /* rns_poly.c:406 */
+size_t Num_decomp(POLY poly);                         /* crt.c:1135 */
+POLY   Decomp(POLY res, POLY poly, uint32_t part);    /* rns_poly.c:74 */
+POLY   Mod_up(POLY res, POLY poly, uint32_t part);    /* rns_poly.c:107 */
+POLY   Decomp_modup(POLY res, POLY poly, uint32_t part); /* rns_poly.c:160 */
+POLY   Mod_down(POLY res, POLY poly);                 /* rns_poly.c:260 */
+POLY   Extend(POLY res, POLY poly);                   /* rns_poly.c:483 */
+/* res = sum_{j<parts} a[j]*b[j] over Q u P limbs    (rns_poly.c:516) */
+POLY   Dot_prod(POLY res, POLY a, POLY b, size_t parts);
+/* res[i] = poly[order[i]] on every limb             (rns_poly.c:1056) */
+POLY   Automorphism_transform(POLY res, POLY poly, int64_t* order);
+
+/* ------------------------------------------------------------------------ */
+/* Keys and automorphism tables  (ant/include/ckks/key.h:25-124)             */
+/* ------------------------------------------------------------------------ */
+
+uint32_t Auto_idx(int32_t rot_idx);   /* 5^r mod 2N, number_theory.c:192 */
+int64_t* Auto_order(int32_t rot_idx); /* device table, borrowed */
+SW_KEY   Swk(bool is_rot, int32_t rot_idx);
+POLY     Pk0_at(SW_KEY swk, uint32_t part);
+POLY     Pk1_at(SW_KEY swk, uint32_t part);
+void     Set_pk0(POLY pk, SW_KEY swk, uint32_t part);
+void     Set_pk1(POLY pk, SW_KEY swk, uint32_t part);
+/* Installs one polynomial (which = 0/1) of digit `part` of the relinearisation
+ * key (is_rot = false) or of the rotation key for rot_idx; host holds L Q
+ * limbs followed by K P limbs in NTT form. */
+void Fhert_import_switch_key(bool is_rot, int32_t rot_idx, uint32_t part,
+                             int which, const int64_t* host);
+
+/* ------------------------------------------------------------------------ */
+/* Ciphertext level  (ant/ckks/src/cipher.c, evaluator.c)                    */
+/* ------------------------------------------------------------------------ */
+
+void   Init_ciph_same_scale(CIPHER res, CIPHER a, CIPHER b);      /* cipher.c:36 */
+void   Init_ciph_up_scale(CIPHER res, CIPHER a, CIPHER b);        /* cipher.c:96 */
+void   Init_ciph_down_scale(CIPHER res, CIPHER a);                /* cipher.c:131 */
+void   Init_ciph3_up_scale(CIPHER3 res, CIPHER a, CIPHER b);      /* cipher.c:118 */
+void   Copy_ciph(CIPHER res, CIPHER ciph);                        /* cipher.c:158 */
+size_t Level(CIPHER ciph);
+void   Free_ciph_poly(CIPHER ciph, uint32_t cnt);
+CIPHER  Add_ciph(CIPHER res, CIPHER a, CIPHER b);       /* evaluator.c:47 */
+CIPHER  Sub_ciph(CIPHER res, CIPHER a, CIPHER b);       /* evaluator.c:118 */
+CIPHER3 Mul_ciph3(CIPHER3 res, CIPHER a, CIPHER b);     /* evaluator.c:137 */
+CIPHER  Relin(CIPHER res, CIPHER3 ciph);                /* evaluator.c:288 */
+CIPHER  Mul_ciph(CIPHER res, CIPHER a, CIPHER b);       /* evaluator.c:177 */
+CIPHER  Rescale_ciph(CIPHER res, CIPHER ciph);          /* evaluator.c:344 */
+CIPHER  Rotate_ciph(CIPHER res, CIPHER ciph, int32_t rot_idx); /* evaluator.c:503-530 */
+CIPHER  Conjugate_ciph(CIPHER res, CIPHER ciph);        /* evaluator.c:568 */
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FHERT_B200_H */

@@ -48,7 +48,7 @@ build_variant() {  # $1 = suffix, rest = extra flags
   done
   wait
   gcc -shared "$@" -o "$OUT/libFHErt_ant_ref$suf.so" "${objs[@]}" -lm \
-      -Wl,--allow-shlib-undefined -Wl,-z,defs
+      -Wl,--allow-shlib-undefined -Wl,-z,defs -Wl,-Bsymbolic
   echo "built $OUT/libFHErt_ant_ref$suf.so"
 }
 
