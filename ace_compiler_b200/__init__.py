@@ -120,6 +120,8 @@ SIGNATURES = {
     "Extend": (POLY, [POLY, POLY]),
     "Dot_prod": (POLY, [POLY, POLY, POLY, C.c_size_t]),
     "Automorphism_transform": (POLY, [POLY, POLY, I64P]),
+    "Fhert_rescale_static": (C.c_int, [I64P, I64P, C.c_size_t]),
+    "Fhert_rescale_static_capacity": (C.c_size_t, []),
     "Auto_idx": (C.c_uint32, [C.c_int32]),
     "Auto_order": (C.c_void_p, [C.c_int32]),
     "Swk": (C.c_void_p, [C.c_bool, C.c_int32]),
