@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <vector>
 
 #include "runtime.h"
 
@@ -31,7 +32,7 @@ int prime_index_of(Context* c, MODULUS* m) {
 LimbBatch single(int prime) {
   LimbBatch b;
   b.count   = 1;
-  b.limb[0] = LimbRef{0, 0, 0, (uint16_t)prime};
+  b.limb[0] = LimbRef{0, 0, 0, (uint8_t)prime, 0};
   return b;
 }
 
@@ -41,13 +42,26 @@ LimbBatch poly_batch(Context* c, POLY res, POLY a, POLY b, size_t level, size_t 
   LimbBatch bt;
   bt.count = 0;
   for (size_t i = 0; i < level; i++)
-    bt.limb[bt.count++] = LimbRef{(uint16_t)i, (uint16_t)i, (uint16_t)i, (uint16_t)i};
+    bt.limb[bt.count++] = LimbRef{(uint16_t)i, (uint16_t)i, (uint16_t)i, (uint8_t)i, 0};
   for (size_t k = 0; k < num_p; k++) {
     LimbRef r;
     r.a     = (uint16_t)(p_offset(a) + k);
     r.b     = (uint16_t)(b ? p_offset(b) + k : 0);
     r.dst   = (uint16_t)(p_offset(res) + k);
-    r.prime = (uint16_t)(c->L + k);
+    r.prime = (uint8_t)(c->L + k);
+    r.sel   = 0;
+    bt.limb[bt.count++] = r;
+  }
+  return bt;
+}
+
+// Appends the limbs of a second polynomial (second base pointer of every
+// operand) to a batch built for the first one.
+LimbBatch both_polys(const LimbBatch& one) {
+  LimbBatch bt = one;
+  for (int i = 0; i < one.count; i++) {
+    LimbRef r = one.limb[i];
+    r.sel     = 7;
     bt.limb[bt.count++] = r;
   }
   return bt;
@@ -239,62 +253,53 @@ uint64_t Fhert_kernel_launches(void) { return ctx_or_null() ? ctx()->launches : 
 void     Fhert_profile_begin(void) { prof_begin(); }
 size_t   Fhert_profile_end(char* buf, size_t cap) { return prof_end(buf, cap); }
 
+
 // ---------------------------------------------------------------------------
 // per-limb vector operations
 // ---------------------------------------------------------------------------
 
-int64_t* Hw_modadd(int64_t* res, int64_t* a, int64_t* b, MODULUS* m, uint32_t degree) {
+static int64_t* hw_binary(EwOp op, int64_t* res, int64_t* a, int64_t* b, int64_t s, MODULUS* m,
+                          uint32_t degree) {
   Context* c = ctx();
   FHERT_ASSERT(degree == c->N, "degree mismatch");
-  launch_elementwise(EW_ADD, res, a, b, 0, single(prime_index_of(c, m)));
+  launch_elementwise(op, ptr2(res), ptr2(a), ptr2(b), s, single(prime_index_of(c, m)));
   return res;
+}
+
+int64_t* Hw_modadd(int64_t* res, int64_t* a, int64_t* b, MODULUS* m, uint32_t degree) {
+  return hw_binary(EW_ADD, res, a, b, 0, m, degree);
 }
 int64_t* Hw_modsub(int64_t* res, int64_t* a, int64_t* b, MODULUS* m, uint32_t degree) {
-  Context* c = ctx();
-  FHERT_ASSERT(degree == c->N, "degree mismatch");
-  launch_elementwise(EW_SUB, res, a, b, 0, single(prime_index_of(c, m)));
-  return res;
+  return hw_binary(EW_SUB, res, a, b, 0, m, degree);
 }
 int64_t* Hw_modmul(int64_t* res, int64_t* a, int64_t* b, MODULUS* m, uint32_t degree) {
-  Context* c = ctx();
-  FHERT_ASSERT(degree == c->N, "degree mismatch");
-  launch_elementwise(EW_MUL, res, a, b, 0, single(prime_index_of(c, m)));
-  return res;
+  return hw_binary(EW_MUL, res, a, b, 0, m, degree);
 }
 int64_t* Hw_modmuladd(int64_t* res, int64_t* a, int64_t* b, MODULUS* m, uint32_t degree) {
-  Context* c = ctx();
-  FHERT_ASSERT(degree == c->N, "degree mismatch");
-  launch_elementwise(EW_MULADD, res, a, b, 0, single(prime_index_of(c, m)));
-  return res;
+  return hw_binary(EW_MULADD, res, a, b, 0, m, degree);
 }
 int64_t* Hw_modadd_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint32_t degree) {
-  Context* c = ctx();
-  FHERT_ASSERT(degree == c->N, "degree mismatch");
-  launch_elementwise(EW_ADD_SCALAR, res, a, nullptr, s, single(prime_index_of(c, m)));
-  return res;
+  return hw_binary(EW_ADD_SCALAR, res, a, a, s, m, degree);
 }
 int64_t* Hw_modmul_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint32_t degree) {
-  Context* c = ctx();
-  FHERT_ASSERT(degree == c->N, "degree mismatch");
-  launch_elementwise(EW_MUL_SCALAR, res, a, nullptr, s, single(prime_index_of(c, m)));
-  return res;
+  return hw_binary(EW_MUL_SCALAR, res, a, a, s, m, degree);
 }
 int64_t* Hw_rotate(int64_t* res, int64_t* val, int64_t* order, MODULUS* m, uint32_t degree) {
   Context* c = ctx();
   FHERT_ASSERT(degree == c->N, "degree mismatch");
   FHERT_ASSERT(res != val, "Hw_rotate cannot work in place");
-  launch_automorphism(res, val, reinterpret_cast<const uint32_t*>(order), single(0));
+  launch_automorphism(ptr2(res), ptr2(val), reinterpret_cast<const uint32_t*>(order), single(0));
   return res;
 }
 void Hw_ntt(int64_t* res, int64_t* val, size_t mod_idx, uint32_t degree) {
   Context* c = ctx();
   FHERT_ASSERT(degree == c->N && mod_idx < c->primes.size(), "Hw_ntt: bad arguments");
-  launch_ntt(val, res, single((int)mod_idx), false);
+  launch_ntt(ptr2(val), ptr2(res), single((int)mod_idx), false);
 }
 void Hw_intt(int64_t* res, int64_t* val, size_t mod_idx, uint32_t degree) {
   Context* c = ctx();
   FHERT_ASSERT(degree == c->N && mod_idx < c->primes.size(), "Hw_intt: bad arguments");
-  launch_ntt(val, res, single((int)mod_idx), true);
+  launch_ntt(ptr2(val), ptr2(res), single((int)mod_idx), true);
 }
 
 // ---------------------------------------------------------------------------
@@ -304,7 +309,7 @@ void Hw_intt(int64_t* res, int64_t* val, size_t mod_idx, uint32_t degree) {
 POLY Conv_poly2ntt_inplace(POLY poly) {
   FHERT_ASSERT(!poly->_is_ntt, "already ntt form");
   Context* c = ctx();
-  launch_ntt(poly->_data, poly->_data,
+  launch_ntt(ptr2(poly->_data), ptr2(poly->_data),
              poly_batch(c, poly, poly, poly, poly->_num_primes, poly->_num_primes_p), false);
   poly->_is_ntt = true;
   return poly;
@@ -313,21 +318,20 @@ POLY Conv_poly2ntt_inplace(POLY poly) {
 POLY Conv_ntt2poly_inplace(POLY poly) {
   FHERT_ASSERT(poly->_is_ntt, "already coefficient form");
   Context* c = ctx();
-  launch_ntt(poly->_data, poly->_data,
+  launch_ntt(ptr2(poly->_data), ptr2(poly->_data),
              poly_batch(c, poly, poly, poly, poly->_num_primes, poly->_num_primes_p), true);
   poly->_is_ntt = false;
   return poly;
 }
 
 static POLY binary_poly(EwOp op, POLY res, POLY a, POLY b) {
-  Context* c = ctx();
-  FHERT_ASSERT(a->_num_primes == b->_num_primes || op == EW_MUL || true, "size");
-  size_t level = res->_num_primes;
+  Context* c     = ctx();
+  size_t   level = res->_num_primes;
   FHERT_ASSERT(level <= a->_num_primes && level <= b->_num_primes, "operand level too low");
   size_t num_p = res->_num_primes_p;
   FHERT_ASSERT(num_p == 0 || (a->_num_primes_p == num_p && b->_num_primes_p == num_p),
                "unmatched special limbs");
-  launch_elementwise(op, res->_data, a->_data, b->_data, 0,
+  launch_elementwise(op, ptr2(res->_data), ptr2(a->_data), ptr2(b->_data), 0,
                      poly_batch(c, res, a, b, level, num_p));
   res->_is_ntt = a->_is_ntt;
   return res;
@@ -352,27 +356,48 @@ POLY Modswitch(POLY res, POLY poly) {
   return res;
 }
 
+// Rescale of one or two polynomials of the same level in NTT form
+// (rns_poly.c:310-404): inverse NTT of the dropped limb(s), centred lift and
+// scaling per remaining limb, forward NTT, combine.  Each step is one launch
+// for all limbs of both polynomials.
+static void rescale_polys(Context* c, int npoly, int64_t* const res[2],
+                          const int64_t* const poly[2], size_t level) {
+  const uint32_t n = c->N;
+  const int      l = (int)level - 1;
+  FHERT_ASSERT(npoly * l <= kMaxLimbs, "rescale batch too large");
+  int64_t*  sc = scratch((size_t)npoly * level * n);  // [npoly] dropped limbs, then lifted limbs
+  LimbBatch lb;
+  lb.count = npoly;
+  for (int g = 0; g < npoly; g++)
+    lb.limb[g] = LimbRef{(uint16_t)l, 0, (uint16_t)g, (uint8_t)l, (uint8_t)g};
+  launch_ntt(ptr2(poly[0], poly[1]), ptr2(sc), lb, true);
+  LimbBatch bt;
+  bt.count = npoly * l;
+  for (int g = 0; g < npoly; g++)
+    for (int i = 0; i < l; i++) {
+      uint16_t t = (uint16_t)(npoly + g * l + i);
+      bt.limb[g * l + i] = LimbRef{t, (uint16_t)g, t, (uint8_t)i, 0};
+    }
+  launch_rescale_lift(ptr2(sc), ptr2(sc), l, bt);
+  launch_ntt(ptr2(sc), ptr2(sc), bt, false);
+  for (int g = 0; g < npoly; g++)
+    for (int i = 0; i < l; i++) {
+      uint8_t sel = (uint8_t)(g ? (1 | 4) : 0);  // poly and res from the second base
+      bt.limb[g * l + i] =
+          LimbRef{(uint16_t)i, (uint16_t)(npoly + g * l + i), (uint16_t)i, (uint8_t)i, sel};
+    }
+  launch_rescale_combine(ptr2(res[0], res[1]), ptr2(poly[0], poly[1]), ptr2(sc), l, bt);
+}
+
 POLY Rescale(POLY res, POLY poly) {
   Context* c     = ctx();
   size_t   level = poly->_num_primes;
   FHERT_ASSERT(level >= 2, "Level of rescale opnd is too small");
   FHERT_ASSERT(res->_num_primes == level && res->_data, "Rescale: primes not match");
   FHERT_ASSERT(poly->_is_ntt, "Rescale: coefficient-form input is not supported");
-  const uint32_t n  = c->N;
-  const int      l  = (int)level - 1;
-  int64_t*       sc = scratch((size_t)level * n);  // [0] = last limb, [1..] = lifted limbs
-  LimbBatch      lb = single(l);
-  lb.limb[0].a      = (uint16_t)l;
-  lb.limb[0].dst    = 0;
-  launch_ntt(poly->_data, sc, lb, true);
-  LimbBatch bt;
-  bt.count = l;
-  for (int i = 0; i < l; i++)
-    bt.limb[i] = LimbRef{(uint16_t)(1 + i), (uint16_t)(1 + i), (uint16_t)(1 + i), (uint16_t)i};
-  launch_rescale_lift(sc, sc, l, bt);
-  launch_ntt(sc, sc, bt, false);
-  for (int i = 0; i < l; i++) bt.limb[i] = LimbRef{(uint16_t)i, (uint16_t)(1 + i), (uint16_t)i, (uint16_t)i};
-  launch_rescale_combine(res->_data, poly->_data, sc, l, bt);
+  int64_t*       r[2] = {res->_data, nullptr};
+  const int64_t* p[2] = {poly->_data, nullptr};
+  rescale_polys(c, 1, r, p, level);
   res->_is_ntt     = true;
   res->_num_primes = level - 1;  // Modswitch(res, res)
   return res;
@@ -404,35 +429,73 @@ POLY Decomp(POLY res, POLY poly, uint32_t part) {
   return res;
 }
 
-// Raises the digit limbs found at src (digit_len limbs, NTT form, limb j of
-// the digit at src + j*N) to all other limbs of `res` (level Q limbs + K P).
-static void raise_digit(Context* c, POLY res, const int64_t* digit_src, size_t level,
-                        uint32_t part, bool is_ntt) {
-  const uint32_t             n     = c->N;
-  const Context::ModUpTable& t     = modup_table(c, (int)level, (int)part);
-  const int                  start = c->alpha * (int)part;
-  int64_t*                   sc    = scratch((size_t)t.digit_len * n);
-  LimbBatch                  in;
-  in.count = t.digit_len;
-  for (int i = 0; i < t.digit_len; i++)
-    in.limb[i] = LimbRef{(uint16_t)i, 0, (uint16_t)i, (uint16_t)(start + i)};
-  const int64_t* coeff = digit_src;
+static void launch_ntt_chunked(Ptr2 in, Ptr2 out, const std::vector<LimbRef>& limbs, bool inverse) {
+  for (size_t off = 0; off < limbs.size(); off += kMaxLimbs) {
+    LimbBatch b;
+    b.count = (int)std::min((size_t)kMaxLimbs, limbs.size() - off);
+    std::copy(limbs.begin() + off, limbs.begin() + off + b.count, b.limb);
+    launch_ntt(in, out, b, inverse);
+  }
+}
+
+// ModUp of digits [part_begin, part_end) of a level-`level` polynomial whose Q
+// limbs start at `src` (rns_poly.c:160-258).  Digit j is raised into the
+// extended polynomial at ext_base + (j - part_begin) * part_stride limbs: its
+// level Q limbs at limb 0.. and its K special limbs at limb p_limb...  Only the
+// complement limbs are written; the digit's own limbs are left to the caller.
+// One inverse-NTT launch, one base-conversion launch and one forward-NTT
+// launch cover all digits.
+static void raise_parts(Context* c, const int64_t* src, bool is_ntt, size_t level,
+                        int part_begin, int part_end, int64_t* ext_base, size_t part_stride,
+                        int p_limb) {
+  const uint32_t n = c->N;
+  const int      K = c->K;
+  const int64_t* coeff = src;
+  int first = part_begin * c->alpha;
+  int last  = std::min(part_end * c->alpha, (int)level);
   if (is_ntt) {
-    launch_ntt(digit_src, sc, in, true);
-    coeff = sc;
+    int64_t* d = scratch(level * n);
+    std::vector<LimbRef> lim;
+    for (int i = first; i < last; i++)
+      lim.push_back(LimbRef{(uint16_t)i, 0, (uint16_t)i, (uint8_t)i, 0});
+    launch_ntt_chunked(ptr2(src), ptr2(d), lim, true);
+    coeff = d;
   }
-  LimbBatch out;
-  out.count = 0;
-  for (int m = 0; m < (int)level; m++) {
-    if (m >= start && m < start + t.digit_len) continue;
-    out.limb[out.count++] = LimbRef{(uint16_t)m, (uint16_t)m, (uint16_t)m, (uint16_t)m};
+  std::vector<LimbRef> out_limbs;
+  for (int pb = part_begin; pb < part_end; pb += kMaxParts) {
+    ConvArgs args;
+    args.groups     = std::min(kMaxParts, part_end - pb);
+    args.level      = (int)level;
+    args.out_total  = (int)level + K;
+    args.p_limb     = p_limb;
+    args.in_stride  = c->L + K;
+    args.out_stride = 1;
+    for (int g = 0; g < args.groups; g++) {
+      int                        part = pb + g;
+      const Context::ModUpTable& t    = modup_table(c, (int)level, part);
+      int                        start = c->alpha * part;
+      ConvGroup&                 cg    = args.g[g];
+      cg.in          = reinterpret_cast<const u64*>(coeff);
+      cg.out         = reinterpret_cast<u64*>(ext_base + (size_t)(part - part_begin) * part_stride * n);
+      cg.inv         = t.d_hat_inv;
+      cg.mat         = t.d_hat_mod;
+      cg.first_limb  = start;
+      cg.first_prime = start;
+      cg.count       = t.digit_len;
+      cg.skip_start  = start;
+      cg.skip_len    = t.digit_len;
+      size_t base_limb = (size_t)(part - part_begin) * part_stride;
+      for (int m = 0; m < (int)level + K; m++) {
+        if (m >= start && m < start + t.digit_len) continue;
+        size_t limb  = base_limb + (m < (int)level ? m : p_limb + (m - (int)level));
+        int    prime = m < (int)level ? m : c->L + (m - (int)level);
+        FHERT_ASSERT(limb < 65536, "extended buffer too large for one launch");
+        out_limbs.push_back(LimbRef{(uint16_t)limb, 0, (uint16_t)limb, (uint8_t)prime, 0});
+      }
+    }
+    launch_base_conv(args);
   }
-  for (int k = 0; k < c->K; k++) {
-    uint16_t off = (uint16_t)(p_offset(res) + k), pr = (uint16_t)(c->L + k);
-    out.limb[out.count++] = LimbRef{off, pr, off, pr};
-  }
-  launch_base_conv(res->_data, coeff, in, out, t.d_hat_inv, t.d_hat_mod, c->L + c->K, 1);
-  if (is_ntt) launch_ntt(res->_data, res->_data, out, false);
+  if (is_ntt) launch_ntt_chunked(ptr2(ext_base), ptr2(ext_base), out_limbs, false);
 }
 
 POLY Decomp_modup(POLY res, POLY poly, uint32_t part) {
@@ -443,7 +506,8 @@ POLY Decomp_modup(POLY res, POLY poly, uint32_t part) {
   size_t start = (size_t)c->alpha * part;
   FHERT_ASSERT(start < level, "Decomp_modup: digit out of range");
   size_t len = std::min((size_t)c->alpha, level - start);
-  raise_digit(c, res, poly->_data + start * c->N, level, part, poly->_is_ntt);
+  raise_parts(c, poly->_data, poly->_is_ntt, level, (int)part, (int)part + 1, res->_data, 0,
+              (int)p_offset(res));
   CUDA_CHECK(cudaMemcpyAsync(res->_data + start * c->N, poly->_data + start * c->N,
                              len * c->N * sizeof(int64_t), cudaMemcpyDeviceToDevice, c->stream));
   res->_is_ntt = poly->_is_ntt;
@@ -451,46 +515,94 @@ POLY Decomp_modup(POLY res, POLY poly, uint32_t part) {
 }
 
 POLY Mod_up(POLY res, POLY old_poly, uint32_t part) {
+  // rns_poly.c:107-158: old_poly holds only the digit's limbs (from Decomp)
   Context* c     = ctx();
   size_t   level = res->_num_primes;
   FHERT_ASSERT(res->_data && res->_num_primes_p == (size_t)c->K, "Mod_up: result size not match");
   size_t start = (size_t)c->alpha * part;
   size_t len   = old_poly->_num_primes;
-  raise_digit(c, res, old_poly->_data, level, part, old_poly->_is_ntt);
+  // place the digit at its own limbs of res, then raise from there
   CUDA_CHECK(cudaMemcpyAsync(res->_data + start * c->N, old_poly->_data,
                              len * c->N * sizeof(int64_t), cudaMemcpyDeviceToDevice, c->stream));
+  raise_parts(c, res->_data, old_poly->_is_ntt, level, (int)part, (int)part + 1, res->_data, 0,
+              (int)p_offset(res));
   res->_is_ntt = old_poly->_is_ntt;
   return res;
 }
 
+// ModDown of one or two extended polynomials of the same level
+// (rns_poly.c:260-308): res[g] = (x[g] - Conv_P->Q(x[g] mod P)) * P^-1, plus
+// add[g] when given.  ext[g] has its special limbs at limb index ext_p_limb.
+static void mod_down_polys(Context* c, int npoly, int64_t* const res[2],
+                           const int64_t* const ext[2], int ext_p_limb,
+                           const int64_t* const add[2], size_t level, bool is_ntt) {
+  const uint32_t n = c->N;
+  const int      K = c->K;
+  FHERT_ASSERT(npoly * (int)level <= kMaxLimbs && npoly * K <= kMaxLimbs, "ModDown batch too large");
+  int64_t* sc   = scratch((size_t)npoly * (K + level) * n);
+  int64_t* conv = sc + (size_t)npoly * K * n;  // [npoly][level]
+  if (is_ntt) {
+    LimbBatch in;
+    in.count = npoly * K;
+    for (int g = 0; g < npoly; g++)
+      for (int k = 0; k < K; k++)
+        in.limb[g * K + k] = LimbRef{(uint16_t)(ext_p_limb + k), 0, (uint16_t)(g * K + k),
+                                     (uint8_t)(c->L + k), (uint8_t)g};
+    launch_ntt(ptr2(ext[0], ext[1]), ptr2(sc), in, true);
+  }
+  ConvArgs args;
+  args.groups     = npoly;
+  args.level      = (int)level;
+  args.out_total  = (int)level;
+  args.p_limb     = 0;
+  args.in_stride  = 1;
+  args.out_stride = K;
+  for (int g = 0; g < npoly; g++) {
+    ConvGroup& cg  = args.g[g];
+    cg.in          = is_ntt ? reinterpret_cast<const u64*>(sc + (size_t)g * K * n)
+                            : reinterpret_cast<const u64*>(ext[g] + (size_t)ext_p_limb * n);
+    cg.out         = reinterpret_cast<u64*>(conv + (size_t)g * level * n);
+    cg.inv         = c->d_phat_inv;
+    cg.mat         = c->d_phat_mod_q;
+    cg.first_limb  = 0;
+    cg.first_prime = c->L;
+    cg.count       = K;
+    cg.skip_start  = 0;
+    cg.skip_len    = 0;
+  }
+  launch_base_conv(args);
+  if (is_ntt) {
+    LimbBatch out;
+    out.count = npoly * (int)level;
+    for (int g = 0; g < npoly; g++)
+      for (int i = 0; i < (int)level; i++) {
+        uint16_t t = (uint16_t)(g * level + i);
+        out.limb[t] = LimbRef{t, 0, t, (uint8_t)i, 0};
+      }
+    launch_ntt(ptr2(conv), ptr2(conv), out, false);
+  }
+  ModDownTail tail;
+  tail.polys = npoly;
+  tail.level = (int)level;
+  for (int g = 0; g < 2; g++) {
+    bool on     = g < npoly;
+    tail.res[g] = on ? reinterpret_cast<u64*>(res[g]) : nullptr;
+    tail.x[g]   = on ? reinterpret_cast<const u64*>(ext[g]) : nullptr;
+    tail.t[g]   = on ? reinterpret_cast<const u64*>(conv + (size_t)g * level * n) : nullptr;
+    tail.add[g] = on && add ? reinterpret_cast<const u64*>(add[g]) : nullptr;
+  }
+  launch_moddown_combine(tail);
+}
+
 POLY Mod_down(POLY res, POLY poly) {
-  Context*       c     = ctx();
-  const uint32_t n     = c->N;
-  size_t         level = poly->_num_primes;
-  if (res->_data == nullptr) Alloc_poly_data(res, n, level, 0);
+  Context* c     = ctx();
+  size_t   level = poly->_num_primes;
+  if (res->_data == nullptr) Alloc_poly_data(res, c->N, level, 0);
   FHERT_ASSERT(res->_num_primes == level && poly->_num_primes_p == (size_t)c->K,
                "Mod_down: result size not match");
-  const int K  = c->K;
-  int64_t*  sc = scratch((size_t)(K + level) * n);  // [0,K) P limbs, [K, K+level) conversions
-  LimbBatch in;
-  in.count = K;
-  for (int k = 0; k < K; k++)
-    in.limb[k] = LimbRef{(uint16_t)(p_offset(poly) + k), 0, (uint16_t)k, (uint16_t)(c->L + k)};
-  const int64_t* coeff = poly->_data;
-  if (poly->_is_ntt) {
-    launch_ntt(poly->_data, sc, in, true);
-    for (int k = 0; k < K; k++) in.limb[k].a = (uint16_t)k;
-    coeff = sc;
-  }
-  LimbBatch out;
-  out.count = (int)level;
-  for (int i = 0; i < (int)level; i++)
-    out.limb[i] = LimbRef{(uint16_t)(K + i), (uint16_t)i, (uint16_t)(K + i), (uint16_t)i};
-  launch_base_conv(sc, coeff, in, out, c->d_phat_inv, c->d_phat_mod_q, 1, K);
-  if (poly->_is_ntt) launch_ntt(sc, sc, out, false);
-  for (int i = 0; i < (int)level; i++)
-    out.limb[i] = LimbRef{(uint16_t)i, (uint16_t)(K + i), (uint16_t)i, (uint16_t)i};
-  launch_moddown_combine(res->_data, poly->_data, sc, out);
+  int64_t*       r[2] = {res->_data, nullptr};
+  const int64_t* x[2] = {poly->_data, nullptr};
+  mod_down_polys(c, 1, r, x, (int)p_offset(poly), nullptr, level, poly->_is_ntt);
   res->_is_ntt = poly->_is_ntt;
   return res;
 }
@@ -501,12 +613,12 @@ POLY Extend(POLY res, POLY poly) {
   FHERT_ASSERT(res->_num_alloc_primes == poly->_num_primes + (size_t)c->K,
                "Extend: alloc_size not match");
   size_t n = c->N;
+  res->_num_primes_p = c->K;
   CUDA_CHECK(cudaMemsetAsync(res->_data + p_offset(res) * n, 0, (size_t)c->K * n * sizeof(int64_t),
                              c->stream));
-  launch_mul_const(res->_data, poly->_data, c->d_p_mod_q,
+  launch_mul_const(ptr2(res->_data), ptr2(poly->_data), c->d_p_mod_q,
                    poly_batch(c, res, poly, nullptr, poly->_num_primes, 0));
-  res->_num_primes_p = c->K;
-  res->_is_ntt       = poly->_is_ntt;
+  res->_is_ntt = poly->_is_ntt;
   return res;
 }
 
@@ -514,18 +626,27 @@ POLY Dot_prod(POLY res, POLY a, POLY b, size_t parts) {
   Context* c = ctx();
   FHERT_ASSERT(parts >= 1 && parts <= (size_t)kMaxParts, "Dot_prod: unsupported digit count");
   size_t level = a[0]._num_primes, num_p = a[0]._num_primes_p;
+  FHERT_ASSERT(num_p == (size_t)c->K, "Dot_prod: operands must be extended polynomials");
   ensure_poly(res, c->N, level, num_p);
   InnerArgs args;
-  args.parts = (int)parts;
+  std::memset(&args, 0, sizeof(args));
+  args.parts      = (int)parts;
+  args.level      = (int)level;
+  args.alpha      = c->alpha;
+  args.key_p_limb = (int)p_offset(&b[0]);
+  args.ext_p_limb = (int)p_offset(&a[0]);
+  args.acc_p_limb = (int)p_offset(res);
+  args.in         = nullptr;
   for (size_t j = 0; j < parts; j++) {
     FHERT_ASSERT(a[j]._num_alloc_primes == a[0]._num_alloc_primes &&
                      b[j]._num_alloc_primes == b[0]._num_alloc_primes,
                  "Dot_prod: operands must share a layout");
-    args.ext[j]  = reinterpret_cast<const u64*>(a[j]._data);
-    args.key0[j] = reinterpret_cast<const u64*>(b[j]._data);
-    args.key1[j] = nullptr;
+    args.ext_ptr[j] = reinterpret_cast<const u64*>(a[j]._data);
+    args.key0[j]    = reinterpret_cast<const u64*>(b[j]._data);
   }
-  launch_inner_product(res->_data, nullptr, args, poly_batch(c, res, &a[0], &b[0], level, num_p));
+  args.acc0 = reinterpret_cast<u64*>(res->_data);
+  args.acc1 = nullptr;
+  launch_inner_product(args);
   res->_is_ntt = a[0]._is_ntt;
   return res;
 }
@@ -534,7 +655,7 @@ POLY Automorphism_transform(POLY res, POLY poly, int64_t* order) {
   Context* c = ctx();
   FHERT_ASSERT(poly->_is_ntt, "Automorphism_transform: coefficient form is not supported");
   FHERT_ASSERT(res->_data != poly->_data, "Automorphism_transform cannot work in place");
-  launch_automorphism(res->_data, poly->_data, reinterpret_cast<const uint32_t*>(order),
+  launch_automorphism(ptr2(res->_data), ptr2(poly->_data), reinterpret_cast<const uint32_t*>(order),
                       poly_batch(c, res, poly, nullptr, poly->_num_primes, poly->_num_primes_p));
   res->_is_ntt = true;
   return res;
@@ -611,6 +732,7 @@ void Fhert_import_switch_key(bool is_rot, int32_t rot_idx, uint32_t part, int wh
   CUDA_CHECK(cudaStreamSynchronize(c->stream));
 }
 
+
 // ---------------------------------------------------------------------------
 // ciphertext level
 // ---------------------------------------------------------------------------
@@ -677,67 +799,71 @@ void Copy_ciph(CIPHER res, CIPHER ciph) {
   Copy_poly(&res->_c1_poly, &ciph->_c1_poly);
 }
 
-CIPHER Add_ciph(CIPHER res, CIPHER a, CIPHER b) {
+static CIPHER add_sub_ciph(EwOp op, CIPHER res, CIPHER a, CIPHER b) {
+  Context* c = ctx();
   Init_ciph_same_scale(res, a, b);
-  Add_poly(&res->_c0_poly, &a->_c0_poly, &b->_c0_poly);
-  Add_poly(&res->_c1_poly, &a->_c1_poly, &b->_c1_poly);
+  size_t level = Level(res), num_p = res->_c0_poly._num_primes_p;
+  FHERT_ASSERT(num_p == 0 || (a->_c0_poly._num_primes_p == num_p && b->_c0_poly._num_primes_p == num_p),
+               "unmatched special limbs");
+  LimbBatch one = poly_batch(c, &res->_c0_poly, &a->_c0_poly, &b->_c0_poly, level, num_p);
+  launch_elementwise(op, ptr2(res->_c0_poly._data, res->_c1_poly._data),
+                     ptr2(a->_c0_poly._data, a->_c1_poly._data),
+                     ptr2(b->_c0_poly._data, b->_c1_poly._data), 0, both_polys(one));
   return res;
 }
 
-CIPHER Sub_ciph(CIPHER res, CIPHER a, CIPHER b) {
-  Init_ciph_same_scale(res, a, b);
-  Sub_poly(&res->_c0_poly, &a->_c0_poly, &b->_c0_poly);
-  Sub_poly(&res->_c1_poly, &a->_c1_poly, &b->_c1_poly);
-  return res;
-}
+CIPHER Add_ciph(CIPHER res, CIPHER a, CIPHER b) { return add_sub_ciph(EW_ADD, res, a, b); }
+CIPHER Sub_ciph(CIPHER res, CIPHER a, CIPHER b) { return add_sub_ciph(EW_SUB, res, a, b); }
 
 CIPHER3 Mul_ciph3(CIPHER3 res, CIPHER a, CIPHER b) {
   // evaluator.c:137-173: c0 = a0*b0, c1 = a0*b1 + a1*b0, c2 = a1*b1
-  Context* c = ctx();
   Init_ciph3_up_scale(res, a, b);
-  size_t  level = res->_c0_poly._num_primes;
-  POLY    r0 = &res->_c0_poly, r1 = &res->_c1_poly, r2 = &res->_c2_poly;
-  Mul_poly(r0, &a->_c0_poly, &b->_c0_poly);
-  Mul_poly(r1, &a->_c0_poly, &b->_c1_poly);
-  launch_elementwise(EW_MULADD, r1->_data, a->_c1_poly._data, b->_c0_poly._data, 0,
-                     poly_batch(c, r1, &a->_c1_poly, &b->_c0_poly, level, 0));
-  Mul_poly(r2, &a->_c1_poly, &b->_c1_poly);
+  size_t level = res->_c0_poly._num_primes;
+  launch_tensor(res->_c0_poly._data, res->_c1_poly._data, res->_c2_poly._data,
+                a->_c0_poly._data, a->_c1_poly._data, b->_c0_poly._data, b->_c1_poly._data,
+                (int)level);
   return res;
 }
 
-// Hybrid key switch of one polynomial (evaluator.c:411-462): digit-wise ModUp,
-// inner product with the key over Q u P, ModDown of both accumulators.
-static void switch_key(Context* c, POLY out0, POLY out1, POLY in, SW_KEY swk) {
+// Hybrid key switch of one polynomial (evaluator.c:411-462): ModUp of all
+// digits, inner product with the key over Q u P, ModDown of both accumulators.
+// out0/out1 receive level limbs; add0/add1 (optional) are added to them, which
+// folds the "+ c0" of a rotation and the "+ c0, + c1" of a relinearisation
+// into the last kernel.  About a dozen launches regardless of the digit count.
+static void switch_key(Context* c, int64_t* out0, int64_t* out1, const int64_t* in, size_t level,
+                       SW_KEY swk, const int64_t* add0, const int64_t* add1) {
   const uint32_t n     = c->N;
-  size_t         level = in->_num_primes;
-  size_t         parts = Num_decomp(in);
-  FHERT_ASSERT(parts <= (size_t)kMaxParts, "too many digits");
-  std::vector<POLYNOMIAL> ext(parts);
-  for (size_t j = 0; j < parts; j++) {
-    std::memset(&ext[j], 0, sizeof(POLYNOMIAL));
-    Alloc_poly_data(&ext[j], n, level, c->K);
-    Decomp_modup(&ext[j], in, (uint32_t)j);
-  }
-  POLYNOMIAL acc0, acc1;
-  std::memset(&acc0, 0, sizeof(acc0));
-  std::memset(&acc1, 0, sizeof(acc1));
-  Alloc_poly_data(&acc0, n, level, c->K);
-  Alloc_poly_data(&acc1, n, level, c->K);
+  const int      K     = c->K;
+  const int      parts = (int)std::min<size_t>((level + c->alpha - 1) / c->alpha, c->dnum);
+  FHERT_ASSERT(parts <= kMaxParts, "too many digits");
+  const size_t ext_limbs = level + K;
+  int64_t*     buf       = nullptr;  // [parts] extended digits, then two accumulators
+  CUDA_CHECK(cudaMallocAsync(&buf, (size_t)(parts + 2) * ext_limbs * n * sizeof(int64_t), c->stream));
+  int64_t* acc0 = buf + (size_t)parts * ext_limbs * n;
+  int64_t* acc1 = acc0 + ext_limbs * n;
+  raise_parts(c, in, true, level, 0, parts, buf, ext_limbs, (int)level);
   InnerArgs args;
-  args.parts = (int)parts;
-  for (size_t j = 0; j < parts; j++) {
-    args.ext[j]  = reinterpret_cast<const u64*>(ext[j]._data);
-    args.key0[j] = reinterpret_cast<const u64*>(swk->_parts[j]._p0._data);
-    args.key1[j] = reinterpret_cast<const u64*>(swk->_parts[j]._p1._data);
+  std::memset(&args, 0, sizeof(args));
+  args.parts      = parts;
+  args.level      = (int)level;
+  args.alpha      = c->alpha;
+  args.key_p_limb = c->L;
+  args.ext_p_limb = (int)level;
+  args.acc_p_limb = (int)level;
+  args.in         = reinterpret_cast<const u64*>(in);  // digits' own limbs come from the input
+  for (int j = 0; j < parts; j++) {
+    args.ext_ptr[j] = reinterpret_cast<const u64*>(buf + (size_t)j * ext_limbs * n);
+    args.key0[j]    = reinterpret_cast<const u64*>(swk->_parts[j]._p0._data);
+    args.key1[j]    = reinterpret_cast<const u64*>(swk->_parts[j]._p1._data);
   }
-  launch_inner_product(acc0._data, acc1._data, args,
-                       poly_batch(c, &acc0, &ext[0], &swk->_parts[0]._p0, level, c->K));
-  acc0._is_ntt = acc1._is_ntt = true;
-  Mod_down(out0, &acc0);
-  Mod_down(out1, &acc1);
-  for (size_t j = 0; j < parts; j++) Free_poly_data(&ext[j]);
-  Free_poly_data(&acc0);
-  Free_poly_data(&acc1);
+  args.acc0 = reinterpret_cast<u64*>(acc0);
+  args.acc1 = reinterpret_cast<u64*>(acc1);
+  launch_inner_product(args);
+  int64_t*       r[2] = {out0, out1};
+  const int64_t* x[2] = {acc0, acc1};
+  const int64_t* a[2] = {add0, add1};
+  mod_down_polys(c, 2, r, x, (int)level, a, level, true);
+  CUDA_CHECK(cudaFreeAsync(buf, c->stream));
 }
 
 CIPHER Relin(CIPHER res, CIPHER3 ciph) {
@@ -745,9 +871,8 @@ CIPHER Relin(CIPHER res, CIPHER3 ciph) {
   Context* c     = ctx();
   size_t   level = ciph->_c2_poly._num_primes;
   init_ciph(res, c->N, level, 0, ciph->_scaling_factor, ciph->_sf_degree, ciph->_slots);
-  switch_key(c, &res->_c0_poly, &res->_c1_poly, &ciph->_c2_poly, Swk(false, 0));
-  Add_poly(&res->_c0_poly, &res->_c0_poly, &ciph->_c0_poly);
-  Add_poly(&res->_c1_poly, &res->_c1_poly, &ciph->_c1_poly);
+  switch_key(c, res->_c0_poly._data, res->_c1_poly._data, ciph->_c2_poly._data, level,
+             Swk(false, 0), ciph->_c0_poly._data, ciph->_c1_poly._data);
   return res;
 }
 
@@ -764,31 +889,34 @@ CIPHER Mul_ciph(CIPHER res, CIPHER a, CIPHER b) {
 
 CIPHER Rescale_ciph(CIPHER res, CIPHER ciph) {
   // evaluator.c:344-363
-  size_t level = Level(ciph);
+  Context* c     = ctx();
+  size_t   level = Level(ciph);
   FHERT_ASSERT(level > 1, "rescale: multiply level is not big enough");
+  FHERT_ASSERT(ciph->_c0_poly._is_ntt, "Rescale_ciph: coefficient form is not supported");
   init_ciph(res, ciph->_c0_poly._ring_degree, level, 0,
             ciph->_scaling_factor / Get_default_sc(), ciph->_sf_degree - 1, ciph->_slots);
-  Rescale(&res->_c0_poly, &ciph->_c0_poly);
-  Rescale(&res->_c1_poly, &ciph->_c1_poly);
+  int64_t*       r[2] = {res->_c0_poly._data, res->_c1_poly._data};
+  const int64_t* p[2] = {ciph->_c0_poly._data, ciph->_c1_poly._data};
+  rescale_polys(c, 2, r, p, level);
+  res->_c0_poly._num_primes = res->_c1_poly._num_primes = level - 1;
   return res;
 }
 
 static CIPHER rotate_with_key(CIPHER res, CIPHER ciph, int32_t rot_idx, uint32_t k) {
   // evaluator.c:503-522: key switch c1, add c0, then permute both polynomials
-  Context*   c     = ctx();
-  size_t     level = Level(ciph);
-  CIPHERTEXT t;
-  std::memset(&t, 0, sizeof(t));
-  init_ciph(&t, c->N, level, 0, ciph->_scaling_factor, ciph->_sf_degree, ciph->_slots);
-  switch_key(c, &t._c0_poly, &t._c1_poly, &ciph->_c1_poly, Swk(true, rot_idx));
-  Add_poly(&t._c0_poly, &t._c0_poly, &ciph->_c0_poly);
+  Context* c     = ctx();
+  size_t   level = Level(ciph);
+  size_t   words = level * c->N;
+  int64_t* t     = nullptr;
+  CUDA_CHECK(cudaMallocAsync(&t, 2 * words * sizeof(int64_t), c->stream));
+  switch_key(c, t, t + words, ciph->_c1_poly._data, level, Swk(true, rot_idx),
+             ciph->_c0_poly._data, nullptr);
   if (res != ciph)
     init_ciph(res, c->N, level, 0, ciph->_scaling_factor, ciph->_sf_degree, ciph->_slots);
-  int64_t* order = reinterpret_cast<int64_t*>(auto_table(c, k));
-  Automorphism_transform(&res->_c0_poly, &t._c0_poly, order);
-  Automorphism_transform(&res->_c1_poly, &t._c1_poly, order);
-  Free_poly_data(&t._c0_poly);
-  Free_poly_data(&t._c1_poly);
+  LimbBatch one = poly_batch(c, &res->_c0_poly, &res->_c0_poly, nullptr, level, 0);
+  launch_automorphism(ptr2(res->_c0_poly._data, res->_c1_poly._data), ptr2(t, t + words),
+                      auto_table(c, k), both_polys(one));
+  CUDA_CHECK(cudaFreeAsync(t, c->stream));
   return res;
 }
 

@@ -362,8 +362,10 @@ Context* create_context(const CKKS_PARAMS* p) {
   const int total = c->L + c->K;
   FHERT_ASSERT(total <= kMaxLimbs, "too many limbs (%d)", total);
   c->moduli.resize(total);
+  c->primes_below_2_60 = std::getenv("FHERT_NO_FAST_ACC") == nullptr;
   for (int i = 0; i < total; i++) {
     FHERT_ASSERT(c->primes[i] < (1ull << 61), "primes must be below 2^61");
+    if (c->primes[i] >= (1ull << 60)) c->primes_below_2_60 = false;
     init_modulus(&c->moduli[i], c->primes[i]);
   }
 
@@ -500,7 +502,7 @@ void destroy_context() {
 const char* const kKernelNames[KID_COUNT] = {
     "ntt_strided", "ntt_contig", "ntt_small", "intt_strided", "intt_contig", "intt_small",
     "elementwise", "automorphism", "mul_const", "rescale_lift", "rescale_combine",
-    "base_conv", "moddown_combine", "inner_product", "mod_raise"};
+    "base_conv", "moddown_combine", "inner_product", "mod_raise", "tensor"};
 
 struct ProfState {
   bool                                    on = false;

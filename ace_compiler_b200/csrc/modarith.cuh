@@ -86,6 +86,42 @@ __device__ __forceinline__ void mac_128(u64& hi, u64& lo, u64 a, u64 b) {
   hi += ph + (lo < pl);
 }
 
+// Lazy 64x64 multiply-accumulate on 30-bit halves, for operands below 2^60.
+// With a = a1*2^30 + a0 and b = b1*2^30 + b0 (all halves below 2^30) the four
+// partial products are below 2^60 and are summed in four separate 64-bit
+// accumulators, one IMAD.WIDE each and no carry handling:
+//   s00 += a0*b0, s01 += a0*b1, s10 += a1*b0, s11 += a1*b1.
+// Up to 16 terms fit.  acc4_fold rebuilds the 128-bit sum
+//   hi:lo = s11*2^60 + (s01 + s10)*2^30 + s00.
+struct Acc4 {
+  u64 s00, s01, s10, s11;
+};
+
+__device__ __forceinline__ void acc4_zero(Acc4& c) { c.s00 = c.s01 = c.s10 = c.s11 = 0; }
+
+__device__ __forceinline__ void acc4_mac(Acc4& c, u64 a, u64 b) {
+  uint32_t a0 = (uint32_t)a & 0x3fffffffu, a1 = (uint32_t)(a >> 30);
+  uint32_t b0 = (uint32_t)b & 0x3fffffffu, b1 = (uint32_t)(b >> 30);
+  c.s00 += (u64)a0 * b0;
+  c.s01 += (u64)a0 * b1;
+  c.s10 += (u64)a1 * b0;
+  c.s11 += (u64)a1 * b1;
+}
+
+__device__ __forceinline__ void acc4_add_shifted(u64& hi, u64& lo, u64 v, int sh) {
+  u64 t = v << sh;
+  lo += t;
+  hi += (v >> (64 - sh)) + (lo < t);
+}
+
+__device__ __forceinline__ void acc4_fold(const Acc4& c, u64& hi, u64& lo) {
+  lo = c.s00;
+  hi = 0;
+  acc4_add_shifted(hi, lo, c.s01, 30);
+  acc4_add_shifted(hi, lo, c.s10, 30);
+  acc4_add_shifted(hi, lo, c.s11, 60);
+}
+
 // Centred lift of a residue mod q_old into [0, q_new)  (modular.h:296-322):
 // values above floor(q_old/2) stand for negative numbers, so the result is
 // (v mod q_new) or (v - q_old mod q_new).  old_mod_new = q_old mod q_new.

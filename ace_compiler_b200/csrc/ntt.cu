@@ -146,7 +146,7 @@ __device__ __forceinline__ int swz(int i) {
 
 template <bool INV>
 __global__ void __launch_bounds__(kBlocksPerCta * 32)
-ntt_contig_kernel(const u64* __restrict__ in, u64* __restrict__ out, LimbBatch batch,
+ntt_contig_kernel(Ptr2 in, Ptr2 out, LimbBatch batch,
                   const Twiddle* __restrict__ tables, const DevModulus* __restrict__ mods,
                   const Twiddle* __restrict__ inv_last, uint32_t n, int logn) {
   __shared__ u64 sm[kBlocksPerCta * kContigBlock];
@@ -157,8 +157,8 @@ ntt_contig_kernel(const u64* __restrict__ in, u64* __restrict__ out, LimbBatch b
   const int      g     = threadIdx.x & 31;
   const uint32_t blk   = blockIdx.x * kBlocksPerCta + warp;  // block in limb
   const size_t   off   = (size_t)blk * kContigBlock;
-  const u64*     src   = in + (size_t)lr.a * n + off;
-  u64*           dst   = out + (size_t)lr.dst * n + off;
+  const u64*     src   = in.p[lr.sel & 1] + (size_t)lr.a * n + off;
+  u64*           dst   = out.p[(lr.sel >> 2) & 1] + (size_t)lr.dst * n + off;
   u64*           s     = sm + warp * kContigBlock;
   const int      s0    = logn - kContigLog;
   // the last inverse stage lives here only when the whole transform is 256
@@ -220,8 +220,7 @@ ntt_contig_kernel(const u64* __restrict__ in, u64* __restrict__ out, LimbBatch b
 // ---- strided columns (global stages 0 .. logN-9) ---------------------------
 
 template <bool INV>
-__global__ void ntt_strided_kernel(const u64* __restrict__ in, u64* __restrict__ out,
-                                   LimbBatch batch, const Twiddle* __restrict__ tables,
+__global__ void ntt_strided_kernel(Ptr2 in, Ptr2 out, LimbBatch batch, const Twiddle* __restrict__ tables,
                                    const DevModulus* __restrict__ mods,
                                    const Twiddle* __restrict__ inv_last, uint32_t n,
                                    int logn) {
@@ -234,8 +233,8 @@ __global__ void ntt_strided_kernel(const u64* __restrict__ in, u64* __restrict__
   const int      c     = threadIdx.x & (kTileCols - 1);
   const int      g     = threadIdx.x >> 4;        // 0 .. 2^(s1-3)-1
   const size_t   col   = (size_t)blockIdx.x * kTileCols + c;
-  const u64*     src   = in + (size_t)lr.a * n + col;
-  u64*           dst   = out + (size_t)lr.dst * n + col;
+  const u64*     src   = in.p[lr.sel & 1] + (size_t)lr.a * n + col;
+  u64*           dst   = out.p[(lr.sel >> 2) & 1] + (size_t)lr.dst * n + col;
   u64            x[8];
 
   // rounds cover local stages [l0, l0+R); forward ascending, inverse descending
@@ -309,8 +308,7 @@ __global__ void ntt_strided_kernel(const u64* __restrict__ in, u64* __restrict__
 // ---- small transforms: whole limb in shared memory -------------------------
 
 template <bool INV>
-__global__ void ntt_small_kernel(const u64* __restrict__ in, u64* __restrict__ out,
-                                 LimbBatch batch, const Twiddle* __restrict__ tables,
+__global__ void ntt_small_kernel(Ptr2 in, Ptr2 out, LimbBatch batch, const Twiddle* __restrict__ tables,
                                  const DevModulus* __restrict__ mods,
                                  const Twiddle* __restrict__ inv_last, uint32_t n,
                                  int logn) {
@@ -319,8 +317,8 @@ __global__ void ntt_small_kernel(const u64* __restrict__ in, u64* __restrict__ o
   const u64      q   = mods[lr.prime].q;
   const Twiddle* tw  = tables + (size_t)lr.prime * n;
   const Twiddle* fin = inv_last + (size_t)lr.prime * 2;
-  const u64*     src = in + (size_t)lr.a * n;
-  u64*           dst = out + (size_t)lr.dst * n;
+  const u64*     src = in.p[lr.sel & 1] + (size_t)lr.a * n;
+  u64*           dst = out.p[(lr.sel >> 2) & 1] + (size_t)lr.dst * n;
   for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) sm_dyn[i] = src[i];
   __syncthreads();
   const uint32_t half = n >> 1;
@@ -367,7 +365,7 @@ __global__ void ntt_small_kernel(const u64* __restrict__ in, u64* __restrict__ o
 constexpr int kSmallMaxLog = 12;
 
 template <bool INV>
-void launch_dir(const u64* in, u64* out, const LimbBatch& b) {
+void launch_dir(Ptr2 in, Ptr2 out, const LimbBatch& b) {
   Context*       c   = ctx();
   const Twiddle* tab = INV ? c->d_inv : c->d_fwd;
   const int      logn = (int)c->logN;
@@ -402,7 +400,10 @@ void launch_dir(const u64* in, u64* out, const LimbBatch& b) {
     prof_after(KID_NTT_STRIDED, b.count);
     // second pass works in place on `out`
     LimbBatch b2 = b;
-    for (int i = 0; i < b2.count; i++) b2.limb[i].a = b2.limb[i].dst;
+    for (int i = 0; i < b2.count; i++) {
+      b2.limb[i].a   = b2.limb[i].dst;
+      b2.limb[i].sel = (uint8_t)((b2.limb[i].sel & 4) | ((b2.limb[i].sel >> 2) & 1));
+    }
     prof_before(KID_NTT_CONTIG);
     ntt_contig_kernel<false><<<grid_c, kBlocksPerCta * 32, 0, c->stream>>>(
         out, out, b2, tab, c->d_mod, c->d_inv_last, c->N, logn);
@@ -413,7 +414,10 @@ void launch_dir(const u64* in, u64* out, const LimbBatch& b) {
         in, out, b, tab, c->d_mod, c->d_inv_last, c->N, logn);
     prof_after(KID_INTT_CONTIG, b.count);
     LimbBatch b2 = b;
-    for (int i = 0; i < b2.count; i++) b2.limb[i].a = b2.limb[i].dst;
+    for (int i = 0; i < b2.count; i++) {
+      b2.limb[i].a   = b2.limb[i].dst;
+      b2.limb[i].sel = (uint8_t)((b2.limb[i].sel & 4) | ((b2.limb[i].sel >> 2) & 1));
+    }
     prof_before(KID_INTT_STRIDED);
     ntt_strided_kernel<true><<<grid_s, threads_s, smem_s, c->stream>>>(
         out, out, b2, tab, c->d_mod, c->d_inv_last, c->N, logn);
@@ -425,12 +429,12 @@ void launch_dir(const u64* in, u64* out, const LimbBatch& b) {
 
 }  // namespace
 
-void launch_ntt(const int64_t* in, int64_t* out, const LimbBatch& b, bool inverse) {
+void launch_ntt(Ptr2 in, Ptr2 out, const LimbBatch& b, bool inverse) {
   if (b.count == 0) return;
   if (inverse)
-    launch_dir<true>(reinterpret_cast<const u64*>(in), reinterpret_cast<u64*>(out), b);
+    launch_dir<true>(in, out, b);
   else
-    launch_dir<false>(reinterpret_cast<const u64*>(in), reinterpret_cast<u64*>(out), b);
+    launch_dir<false>(in, out, b);
 }
 
 }  // namespace fhert

@@ -1,7 +1,10 @@
 // Element-wise, permutation, rescale, base-conversion and key inner-product
-// kernels over limb-major RNS polynomials.  Every kernel takes a LimbBatch so
-// that one launch covers all limbs of an operation; the x dimension of the
-// grid walks the N coefficients of a limb, the y dimension the limbs.
+// kernels over limb-major RNS polynomials.  Kernels take a LimbBatch (or a
+// compact group descriptor) so that one launch covers all limbs -- and, for a
+// ciphertext, both polynomials -- of an operation; the x dimension of the grid
+// walks the N coefficients of a limb, the y dimension the limbs.
+#include <algorithm>
+
 #include "runtime.h"
 
 namespace fhert {
@@ -15,17 +18,27 @@ inline dim3 grid_for(uint32_t n, int per_thread, int limbs) {
   return dim3((n + per_block - 1) / per_block, limbs);
 }
 
+__device__ __forceinline__ const u64* sel_a(const Ptr2& p, const LimbRef& lr, uint32_t n) {
+  return p.p[lr.sel & 1] + (size_t)lr.a * n;
+}
+__device__ __forceinline__ const u64* sel_b(const Ptr2& p, const LimbRef& lr, uint32_t n) {
+  return p.p[(lr.sel >> 1) & 1] + (size_t)lr.b * n;
+}
+__device__ __forceinline__ u64* sel_d(const Ptr2& p, const LimbRef& lr, uint32_t n) {
+  return p.p[(lr.sel >> 2) & 1] + (size_t)lr.dst * n;
+}
+
 // ---- element-wise (hal/src/hal.c:15-121, poly/src/rns_poly.c:852-1054) ------
 
 template <int OP>
 __global__ void __launch_bounds__(kThreads)
-ew_kernel(u64* __restrict__ res, const u64* __restrict__ a, const u64* __restrict__ b,
-          u64 scalar, LimbBatch batch, const DevModulus* __restrict__ mods, uint32_t n) {
+ew_kernel(Ptr2 res, Ptr2 a, Ptr2 b, u64 scalar, LimbBatch batch,
+          const DevModulus* __restrict__ mods, uint32_t n) {
   const LimbRef    lr = batch.limb[blockIdx.y];
   const DevModulus m  = mods[lr.prime];
-  const u64*       pa = a + (size_t)lr.a * n;
-  const u64*       pb = b ? b + (size_t)lr.b * n : nullptr;
-  u64*             pr = res + (size_t)lr.dst * n;
+  const u64*       pa = sel_a(a, lr, n);
+  const u64*       pb = sel_b(b, lr, n);
+  u64*             pr = sel_d(res, lr, n);
   u64              sc = 0;
   if (OP == EW_ADD_SCALAR || OP == EW_MUL_SCALAR) {
     // scalars arrive as signed 64-bit values; bring into [0, q)
@@ -47,135 +60,227 @@ ew_kernel(u64* __restrict__ res, const u64* __restrict__ a, const u64* __restric
 // ---- automorphism in NTT form: a pure gather (hal.c:123-138) ----------------
 
 __global__ void __launch_bounds__(kThreads)
-automorphism_kernel(u64* __restrict__ res, const u64* __restrict__ val,
-                    const uint32_t* __restrict__ table, LimbBatch batch, uint32_t n) {
+automorphism_kernel(Ptr2 res, Ptr2 val, const uint32_t* __restrict__ table, LimbBatch batch,
+                    uint32_t n) {
   const LimbRef lr = batch.limb[blockIdx.y];
-  const u64*    pv = val + (size_t)lr.a * n;
-  u64*          pr = res + (size_t)lr.dst * n;
+  const u64*    pv = sel_a(val, lr, n);
+  u64*          pr = sel_d(res, lr, n);
   for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads)
     pr[i] = pv[__ldg(table + i)];
 }
 
 __global__ void __launch_bounds__(kThreads)
-mul_const_kernel(u64* __restrict__ res, const u64* __restrict__ val,
-                 const Twiddle* __restrict__ consts, LimbBatch batch,
+mul_const_kernel(Ptr2 res, Ptr2 val, const Twiddle* __restrict__ consts, LimbBatch batch,
                  const DevModulus* __restrict__ mods, uint32_t n) {
   const LimbRef lr = batch.limb[blockIdx.y];
   const u64     q  = mods[lr.prime].q;
   const Twiddle c  = consts[lr.prime];
-  const u64*    pv = val + (size_t)lr.a * n;
-  u64*          pr = res + (size_t)lr.dst * n;
+  const u64*    pv = sel_a(val, lr, n);
+  u64*          pr = sel_d(res, lr, n);
   for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads)
     pr[i] = mul_shoup(pv[i], c.w, c.wp, q);
+}
+
+// ---- tensor product (ckks/src/evaluator.c:137-173) ---------------------------
+// limb index = prime index = blockIdx.y; the middle term is summed in 128 bits
+// and reduced once.
+
+__global__ void __launch_bounds__(kThreads)
+tensor_kernel(u64* __restrict__ d0, u64* __restrict__ d1, u64* __restrict__ d2,
+              const u64* __restrict__ a0, const u64* __restrict__ a1,
+              const u64* __restrict__ b0, const u64* __restrict__ b1,
+              const DevModulus* __restrict__ mods, uint32_t n) {
+  const DevModulus m   = mods[blockIdx.y];
+  const size_t     off = (size_t)blockIdx.y * n;
+  for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads) {
+    u64 x0 = a0[off + i], x1 = a1[off + i], y0 = b0[off + i], y1 = b1[off + i];
+    d0[off + i] = mul_mod(x0, y0, m);
+    d2[off + i] = mul_mod(x1, y1, m);
+    u64 hi = 0, lo = 0;
+    mac_128(hi, lo, x0, y1);
+    mac_128(hi, lo, x1, y0);
+    d1[off + i] = reduce_128(hi, lo, m);
+  }
 }
 
 // ---- rescale (rns_poly.c:351-383) -------------------------------------------
 
 __global__ void __launch_bounds__(kThreads)
-rescale_lift_kernel(u64* __restrict__ tmp, const u64* __restrict__ last, u64 q_last,
-                    const Twiddle* __restrict__ neg_row, const u64* __restrict__ mod_row,
-                    LimbBatch batch, const DevModulus* __restrict__ mods, uint32_t n) {
+rescale_lift_kernel(Ptr2 tmp, Ptr2 last, u64 q_last, const Twiddle* __restrict__ neg_row,
+                    const u64* __restrict__ mod_row, LimbBatch batch,
+                    const DevModulus* __restrict__ mods, uint32_t n) {
   const LimbRef    lr = batch.limb[blockIdx.y];
   const DevModulus m  = mods[lr.prime];
   const Twiddle    w  = neg_row[lr.prime];
   const u64        om = mod_row[lr.prime];
-  u64*             pt = tmp + (size_t)lr.dst * n;
+  const u64*       pl = sel_b(last, lr, n);
+  u64*             pt = sel_d(tmp, lr, n);
   for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads) {
-    u64 s = switch_modulus(last[i], q_last, m, om);
+    u64 s = switch_modulus(pl[i], q_last, m, om);
     pt[i] = mul_shoup(s, w.w, w.wp, m.q);
   }
 }
 
 __global__ void __launch_bounds__(kThreads)
-rescale_combine_kernel(u64* __restrict__ res, const u64* __restrict__ poly,
-                       const u64* __restrict__ tmp, const Twiddle* __restrict__ inv_row,
+rescale_combine_kernel(Ptr2 res, Ptr2 poly, Ptr2 tmp, const Twiddle* __restrict__ inv_row,
                        LimbBatch batch, const DevModulus* __restrict__ mods, uint32_t n) {
   const LimbRef lr = batch.limb[blockIdx.y];
   const u64     q  = mods[lr.prime].q;
   const Twiddle w  = inv_row[lr.prime];
-  const u64*    pp = poly + (size_t)lr.a * n;
-  const u64*    pt = tmp + (size_t)lr.b * n;
-  u64*          pr = res + (size_t)lr.dst * n;
+  const u64*    pp = sel_a(poly, lr, n);
+  const u64*    pt = sel_b(tmp, lr, n);
+  u64*          pr = sel_d(res, lr, n);
   for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads)
     pr[i] = add_mod(mul_shoup(pp[i], w.w, w.wp, q), pt[i], q);
 }
 
 // ---- approximate base conversion --------------------------------------------
-// One thread per coefficient; y_i kept in registers, the conversion matrix in
-// shared memory.  blockIdx.y selects a chunk of kOutChunk output limbs.
+// One thread per coefficient; the scaled inputs y_i stay in registers (padded
+// with zeros up to NIN), the conversion matrix of the CTA's output chunk sits
+// in shared memory.  blockIdx.y selects the chunk of outputs, blockIdx.z the
+// group (digit for ModUp, polynomial for ModDown).  With FAST the sums use the
+// carry-free 32-bit-half accumulators (all primes below 2^60, NIN <= 16).
 
-constexpr int kOutChunk = 12;
+constexpr int kMaxOutChunk = 18;
 
+template <int NIN, bool FAST>
 __global__ void __launch_bounds__(kThreads)
-base_conv_kernel(u64* __restrict__ out, const u64* __restrict__ in, LimbBatch in_limbs,
-                 LimbBatch out_limbs, const Twiddle* __restrict__ inv,
-                 const u64* __restrict__ mat, int in_stride, int out_stride,
-                 const DevModulus* __restrict__ mods, uint32_t n) {
-  __shared__ u64 sm_mat[kOutChunk * kMaxDigit];
-  const int      nin   = in_limbs.count;
-  const int      o_beg = blockIdx.y * kOutChunk;
-  const int      o_end = min(o_beg + kOutChunk, out_limbs.count);
-  for (int t = threadIdx.x; t < (o_end - o_beg) * nin; t += kThreads) {
-    int o = t / nin, i = t - o * nin;
-    sm_mat[o * kMaxDigit + i] =
-        mat[(size_t)i * in_stride + (size_t)out_limbs.limb[o_beg + o].b * out_stride];
+base_conv_kernel(ConvArgs args, int chunk, int num_q, const DevModulus* __restrict__ mods,
+                 uint32_t n) {
+  __shared__ u64  sm_mat[kMaxOutChunk * NIN];
+  const ConvGroup g         = args.g[blockIdx.z];
+  const int       out_count = args.out_total - g.skip_len;
+  const int       o_beg     = blockIdx.y * chunk;
+  if (o_beg >= out_count) return;
+  const int o_end = min(o_beg + chunk, out_count);
+  for (int t = threadIdx.x; t < (o_end - o_beg) * NIN; t += kThreads) {
+    int o = t / NIN, i = t - o * NIN;
+    int m = o_beg + o;
+    m     = m < g.skip_start ? m : m + g.skip_len;
+    int prime = m < args.level ? m : num_q + (m - args.level);
+    sm_mat[t] = i < g.count
+                    ? g.mat[(size_t)i * args.in_stride + (size_t)prime * args.out_stride]
+                    : 0;
   }
   __syncthreads();
   const uint32_t c = blockIdx.x * kThreads + threadIdx.x;
   if (c >= n) return;
-  u64 y[kMaxDigit];
+  u64 y[NIN];
 #pragma unroll
-  for (int i = 0; i < kMaxDigit; i++) {
-    if (i < nin) {
-      const LimbRef lr = in_limbs.limb[i];
-      const Twiddle w  = inv[i];
-      y[i] = mul_shoup(in[(size_t)lr.a * n + c], w.w, w.wp, mods[lr.prime].q);
+  for (int i = 0; i < NIN; i++) {
+    if (i < g.count) {
+      const Twiddle w = g.inv[i];
+      y[i] = mul_shoup(g.in[(size_t)(g.first_limb + i) * n + c], w.w, w.wp,
+                       mods[g.first_prime + i].q);
+    } else {
+      y[i] = 0;
     }
   }
   for (int o = o_beg; o < o_end; o++) {
-    const LimbRef    lo = out_limbs.limb[o];
-    const DevModulus m  = mods[lo.prime];
-    u64              hi = 0, lw = 0;
+    int m     = o < g.skip_start ? o : o + g.skip_len;
+    int prime = m < args.level ? m : num_q + (m - args.level);
+    int limb  = m < args.level ? m : args.p_limb + (m - args.level);
+    const DevModulus md  = mods[prime];
+    const u64*       row = sm_mat + (o - o_beg) * NIN;
+    u64              hi, lo;
+    if (FAST) {
+      Acc4 acc;
+      acc4_zero(acc);
 #pragma unroll
-    for (int i = 0; i < kMaxDigit; i++)
-      if (i < nin) mac_128(hi, lw, y[i], sm_mat[(o - o_beg) * kMaxDigit + i]);
-    out[(size_t)lo.dst * n + c] = reduce_128(hi, lw, m);
+      for (int i = 0; i < NIN; i++) acc4_mac(acc, y[i], row[i]);
+      acc4_fold(acc, hi, lo);
+    } else {
+      hi = lo = 0;
+#pragma unroll
+      for (int i = 0; i < NIN; i++) mac_128(hi, lo, y[i], row[i]);
+    }
+    g.out[(size_t)limb * n + c] = reduce_128(hi, lo, md);
   }
 }
 
+// ---- ModDown tail (rns_poly.c:293-304), optionally adding a polynomial -------
+
 __global__ void __launch_bounds__(kThreads)
-moddown_combine_kernel(u64* __restrict__ res, const u64* __restrict__ x,
-                       const u64* __restrict__ t, const Twiddle* __restrict__ p_inv,
-                       LimbBatch batch, const DevModulus* __restrict__ mods, uint32_t n) {
-  const LimbRef lr = batch.limb[blockIdx.y];
-  const u64     q  = mods[lr.prime].q;
-  const Twiddle w  = p_inv[lr.prime];
-  const u64*    px = x + (size_t)lr.a * n;
-  const u64*    pt = t + (size_t)lr.b * n;
-  u64*          pr = res + (size_t)lr.dst * n;
-  for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads)
-    pr[i] = mul_shoup(sub_mod(px[i], pt[i], q), w.w, w.wp, q);
+moddown_combine_kernel(ModDownTail a, const Twiddle* __restrict__ p_inv,
+                       const DevModulus* __restrict__ mods, uint32_t n) {
+  const int     g   = blockIdx.z;
+  const u64     q   = mods[blockIdx.y].q;
+  const Twiddle w   = p_inv[blockIdx.y];
+  const size_t  off = (size_t)blockIdx.y * n;
+  const u64*    px  = a.x[g] + off;
+  const u64*    pt  = a.t[g] + off;
+  const u64*    pa  = a.add[g] ? a.add[g] + off : nullptr;
+  u64*          pr  = a.res[g] + off;
+  for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads) {
+    u64 r = mul_shoup(sub_mod(px[i], pt[i], q), w.w, w.wp, q);
+    if (pa) r = add_mod(r, pa[i], q);
+    pr[i] = r;
+  }
 }
 
 // ---- key inner product (rns_poly.c:516, rns_poly_impl.c:13-160) --------------
-// 128-bit accumulation over the digits, one reduction per output word.
+// One reduction per output word; two coefficients per thread (16-byte loads).
 
-template <bool TWO>
+template <bool TWO, bool FAST>
 __global__ void __launch_bounds__(kThreads)
-inner_product_kernel(u64* __restrict__ acc0, u64* __restrict__ acc1, InnerArgs args,
-                     LimbBatch batch, const DevModulus* __restrict__ mods, uint32_t n) {
-  const LimbRef    lr = batch.limb[blockIdx.y];
-  const DevModulus m  = mods[lr.prime];
-  const size_t     oa = (size_t)lr.a * n, ob = (size_t)lr.b * n, od = (size_t)lr.dst * n;
-  for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads) {
-    u64 h0 = 0, l0 = 0, h1 = 0, l1 = 0;
-    for (int j = 0; j < args.parts; j++) {
-      u64 e = args.ext[j][oa + i];
-      mac_128(h0, l0, e, __ldg(args.key0[j] + ob + i));
-      if (TWO) mac_128(h1, l1, e, __ldg(args.key1[j] + ob + i));
+inner_product_kernel(InnerArgs a, int num_q, const DevModulus* __restrict__ mods, uint32_t n) {
+  const int        m     = blockIdx.y;  // limb among level Q limbs then K P limbs
+  const bool       is_q  = m < a.level;
+  const int        prime = is_q ? m : num_q + (m - a.level);
+  const DevModulus md    = mods[prime];
+  const size_t e_off = (size_t)(is_q ? m : a.ext_p_limb + (m - a.level)) * n;
+  const size_t k_off = (size_t)(is_q ? m : a.key_p_limb + (m - a.level)) * n;
+  const size_t d_off = (size_t)(is_q ? m : a.acc_p_limb + (m - a.level)) * n;
+  const int    own   = (a.in != nullptr && is_q) ? m / a.alpha : -1;
+  const uint32_t pairs = n >> 1;
+  for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < pairs; i += gridDim.x * kThreads) {
+    Acc4 c00, c01, c10, c11;
+    u64  h[4] = {0, 0, 0, 0}, l[4] = {0, 0, 0, 0};
+    if (FAST) {
+      acc4_zero(c00);
+      acc4_zero(c01);
+      acc4_zero(c10);
+      acc4_zero(c11);
     }
-    acc0[od + i] = reduce_128(h0, l0, m);
-    if (TWO) acc1[od + i] = reduce_128(h1, l1, m);
+    for (int j = 0; j < a.parts; j++) {
+      const u64* es = (j == own) ? a.in + (size_t)m * n : a.ext_ptr[j] + e_off;
+      ulonglong2 e  = reinterpret_cast<const ulonglong2*>(es)[i];
+      ulonglong2 k0 = __ldg(reinterpret_cast<const ulonglong2*>(a.key0[j] + k_off) + i);
+      if (FAST) {
+        acc4_mac(c00, e.x, k0.x);
+        acc4_mac(c01, e.y, k0.y);
+      } else {
+        mac_128(h[0], l[0], e.x, k0.x);
+        mac_128(h[1], l[1], e.y, k0.y);
+      }
+      if (TWO) {
+        ulonglong2 k1 = __ldg(reinterpret_cast<const ulonglong2*>(a.key1[j] + k_off) + i);
+        if (FAST) {
+          acc4_mac(c10, e.x, k1.x);
+          acc4_mac(c11, e.y, k1.y);
+        } else {
+          mac_128(h[2], l[2], e.x, k1.x);
+          mac_128(h[3], l[3], e.y, k1.y);
+        }
+      }
+    }
+    if (FAST) {
+      acc4_fold(c00, h[0], l[0]);
+      acc4_fold(c01, h[1], l[1]);
+      if (TWO) {
+        acc4_fold(c10, h[2], l[2]);
+        acc4_fold(c11, h[3], l[3]);
+      }
+    }
+    ulonglong2 r;
+    r.x = reduce_128(h[0], l[0], md);
+    r.y = reduce_128(h[1], l[1], md);
+    reinterpret_cast<ulonglong2*>(a.acc0 + d_off)[i] = r;
+    if (TWO) {
+      r.x = reduce_128(h[2], l[2], md);
+      r.y = reduce_128(h[3], l[3], md);
+      reinterpret_cast<ulonglong2*>(a.acc1 + d_off)[i] = r;
+    }
   }
 }
 
@@ -200,19 +305,16 @@ inline void after_launch(Context* c, KernelId id, int limbs) {
 
 }  // namespace
 
-#define U64P(p) reinterpret_cast<u64*>(p)
-#define CU64P(p) reinterpret_cast<const u64*>(p)
-
-void launch_elementwise(EwOp op, int64_t* res, const int64_t* a, const int64_t* b,
-                        int64_t scalar, const LimbBatch& batch) {
+void launch_elementwise(EwOp op, Ptr2 res, Ptr2 a, Ptr2 b, int64_t scalar,
+                        const LimbBatch& batch) {
   if (batch.count == 0) return;
   Context* c = ctx();
   prof_before(KID_ELEMENTWISE);
-  dim3     g = grid_for(c->N, 2, batch.count);
-#define EW_CASE(OP)                                                                     \
-  case OP:                                                                              \
-    ew_kernel<OP><<<g, kThreads, 0, c->stream>>>(U64P(res), CU64P(a), CU64P(b),         \
-                                                 (u64)scalar, batch, c->d_mod, c->N);   \
+  dim3 g = grid_for(c->N, 2, batch.count);
+#define EW_CASE(OP)                                                                        \
+  case OP:                                                                                 \
+    ew_kernel<OP><<<g, kThreads, 0, c->stream>>>(res, a, b, (u64)scalar, batch, c->d_mod,  \
+                                                 c->N);                                    \
     break;
   switch (op) {
     EW_CASE(EW_ADD)
@@ -226,85 +328,114 @@ void launch_elementwise(EwOp op, int64_t* res, const int64_t* a, const int64_t* 
   after_launch(c, KID_ELEMENTWISE, batch.count);
 }
 
-void launch_automorphism(int64_t* res, const int64_t* val, const uint32_t* table,
-                         const LimbBatch& batch) {
+void launch_automorphism(Ptr2 res, Ptr2 val, const uint32_t* table, const LimbBatch& batch) {
   if (batch.count == 0) return;
   Context* c = ctx();
   prof_before(KID_AUTOMORPHISM);
   automorphism_kernel<<<grid_for(c->N, 2, batch.count), kThreads, 0, c->stream>>>(
-      U64P(res), CU64P(val), table, batch, c->N);
+      res, val, table, batch, c->N);
   after_launch(c, KID_AUTOMORPHISM, batch.count);
 }
 
-void launch_mul_const(int64_t* res, const int64_t* val, const Twiddle* consts,
-                      const LimbBatch& batch) {
+void launch_mul_const(Ptr2 res, Ptr2 val, const Twiddle* consts, const LimbBatch& batch) {
   if (batch.count == 0) return;
   Context* c = ctx();
   prof_before(KID_MUL_CONST);
   mul_const_kernel<<<grid_for(c->N, 2, batch.count), kThreads, 0, c->stream>>>(
-      U64P(res), CU64P(val), consts, batch, c->d_mod, c->N);
+      res, val, consts, batch, c->d_mod, c->N);
   after_launch(c, KID_MUL_CONST, batch.count);
 }
 
-void launch_rescale_lift(int64_t* tmp, const int64_t* last, int l, const LimbBatch& batch) {
+void launch_tensor(int64_t* d0, int64_t* d1, int64_t* d2, const int64_t* a0,
+                   const int64_t* a1, const int64_t* b0, const int64_t* b1, int level) {
+  if (level == 0) return;
+  Context* c = ctx();
+  prof_before(KID_TENSOR);
+  tensor_kernel<<<grid_for(c->N, 2, level), kThreads, 0, c->stream>>>(
+      (u64*)d0, (u64*)d1, (u64*)d2, (const u64*)a0, (const u64*)a1, (const u64*)b0,
+      (const u64*)b1, c->d_mod, c->N);
+  after_launch(c, KID_TENSOR, level);
+}
+
+void launch_rescale_lift(Ptr2 tmp, Ptr2 last, int l, const LimbBatch& batch) {
   if (batch.count == 0) return;
   Context* c = ctx();
   prof_before(KID_RESCALE_LIFT);
   rescale_lift_kernel<<<grid_for(c->N, 2, batch.count), kThreads, 0, c->stream>>>(
-      U64P(tmp), CU64P(last), c->primes[l], c->d_ql_neg + (size_t)l * c->L,
-      c->d_ql_mod + (size_t)l * c->L, batch, c->d_mod, c->N);
+      tmp, last, c->primes[l], c->d_ql_neg + (size_t)l * c->L, c->d_ql_mod + (size_t)l * c->L,
+      batch, c->d_mod, c->N);
   after_launch(c, KID_RESCALE_LIFT, batch.count);
 }
 
-void launch_rescale_combine(int64_t* res, const int64_t* poly, const int64_t* tmp, int l,
-                            const LimbBatch& batch) {
+void launch_rescale_combine(Ptr2 res, Ptr2 poly, Ptr2 tmp, int l, const LimbBatch& batch) {
   if (batch.count == 0) return;
   Context* c = ctx();
   prof_before(KID_RESCALE_COMBINE);
   rescale_combine_kernel<<<grid_for(c->N, 2, batch.count), kThreads, 0, c->stream>>>(
-      U64P(res), CU64P(poly), CU64P(tmp), c->d_ql_inv + (size_t)l * c->L, batch, c->d_mod,
-      c->N);
+      res, poly, tmp, c->d_ql_inv + (size_t)l * c->L, batch, c->d_mod, c->N);
   after_launch(c, KID_RESCALE_COMBINE, batch.count);
 }
 
-void launch_base_conv(int64_t* out, const int64_t* in, const LimbBatch& in_limbs,
-                      const LimbBatch& out_limbs, const Twiddle* inv, const u64* mat,
-                      int in_stride, int out_stride) {
-  if (out_limbs.count == 0) return;
-  Context* c = ctx();
-  prof_before(KID_BASE_CONV);
-  FHERT_ASSERT(in_limbs.count <= kMaxDigit, "base conversion from %d limbs unsupported",
-               in_limbs.count);
-  dim3 g((c->N + kThreads - 1) / kThreads, (out_limbs.count + kOutChunk - 1) / kOutChunk);
-  base_conv_kernel<<<g, kThreads, 0, c->stream>>>(U64P(out), CU64P(in), in_limbs, out_limbs,
-                                                  inv, mat, in_stride, out_stride, c->d_mod,
-                                                  c->N);
-  after_launch(c, KID_BASE_CONV, out_limbs.count);
+template <int NIN>
+static void base_conv_dispatch(Context* c, const ConvArgs& args, dim3 grid, int chunk) {
+  if (c->primes_below_2_60)
+    base_conv_kernel<NIN, true><<<grid, kThreads, 0, c->stream>>>(args, chunk, c->L, c->d_mod,
+                                                                  c->N);
+  else
+    base_conv_kernel<NIN, false><<<grid, kThreads, 0, c->stream>>>(args, chunk, c->L, c->d_mod,
+                                                                   c->N);
 }
 
-void launch_moddown_combine(int64_t* res, const int64_t* x, const int64_t* t,
-                            const LimbBatch& batch) {
-  if (batch.count == 0) return;
+void launch_base_conv(const ConvArgs& args) {
+  Context* c = ctx();
+  int max_in = 0, max_out = 0, total_out = 0;
+  for (int g = 0; g < args.groups; g++) {
+    max_in  = std::max(max_in, args.g[g].count);
+    max_out = std::max(max_out, args.out_total - args.g[g].skip_len);
+    total_out += args.out_total - args.g[g].skip_len;
+  }
+  if (max_out <= 0 || args.groups == 0) return;
+  FHERT_ASSERT(max_in <= kMaxDigit, "base conversion from %d limbs unsupported", max_in);
+  int  chunks = (max_out + kMaxOutChunk - 1) / kMaxOutChunk;
+  int  chunk  = (max_out + chunks - 1) / chunks;
+  dim3 grid((c->N + kThreads - 1) / kThreads, chunks, args.groups);
+  prof_before(KID_BASE_CONV);
+  if (max_in <= 2) base_conv_dispatch<2>(c, args, grid, chunk);
+  else if (max_in <= 4) base_conv_dispatch<4>(c, args, grid, chunk);
+  else if (max_in <= 6) base_conv_dispatch<6>(c, args, grid, chunk);
+  else if (max_in <= 8) base_conv_dispatch<8>(c, args, grid, chunk);
+  else if (max_in <= 12) base_conv_dispatch<12>(c, args, grid, chunk);
+  else base_conv_dispatch<16>(c, args, grid, chunk);
+  after_launch(c, KID_BASE_CONV, total_out);
+}
+
+void launch_moddown_combine(const ModDownTail& args) {
+  if (args.level == 0 || args.polys == 0) return;
   Context* c = ctx();
   prof_before(KID_MODDOWN_COMBINE);
-  moddown_combine_kernel<<<grid_for(c->N, 2, batch.count), kThreads, 0, c->stream>>>(
-      U64P(res), CU64P(x), CU64P(t), c->d_p_inv, batch, c->d_mod, c->N);
-  after_launch(c, KID_MODDOWN_COMBINE, batch.count);
+  dim3 g = grid_for(c->N, 2, args.level);
+  g.z    = args.polys;
+  moddown_combine_kernel<<<g, kThreads, 0, c->stream>>>(args, c->d_p_inv, c->d_mod, c->N);
+  after_launch(c, KID_MODDOWN_COMBINE, args.level * args.polys);
 }
 
-void launch_inner_product(int64_t* acc0, int64_t* acc1, const InnerArgs& args,
-                          const LimbBatch& batch) {
-  if (batch.count == 0) return;
-  Context* c = ctx();
+void launch_inner_product(const InnerArgs& args) {
+  Context* c     = ctx();
+  int      limbs = args.level + c->K;
+  FHERT_ASSERT(args.parts >= 1 && args.parts <= kMaxParts, "unsupported digit count");
   prof_before(KID_INNER_PRODUCT);
-  dim3     g = grid_for(c->N, 2, batch.count);
-  if (acc1)
-    inner_product_kernel<true><<<g, kThreads, 0, c->stream>>>(U64P(acc0), U64P(acc1), args,
-                                                              batch, c->d_mod, c->N);
+  dim3 g    = grid_for(c->N, 4, limbs);
+  bool fast = c->primes_below_2_60;
+  bool two  = args.acc1 != nullptr;
+  if (two && fast)
+    inner_product_kernel<true, true><<<g, kThreads, 0, c->stream>>>(args, c->L, c->d_mod, c->N);
+  else if (two)
+    inner_product_kernel<true, false><<<g, kThreads, 0, c->stream>>>(args, c->L, c->d_mod, c->N);
+  else if (fast)
+    inner_product_kernel<false, true><<<g, kThreads, 0, c->stream>>>(args, c->L, c->d_mod, c->N);
   else
-    inner_product_kernel<false><<<g, kThreads, 0, c->stream>>>(U64P(acc0), nullptr, args,
-                                                               batch, c->d_mod, c->N);
-  after_launch(c, KID_INNER_PRODUCT, batch.count);
+    inner_product_kernel<false, false><<<g, kThreads, 0, c->stream>>>(args, c->L, c->d_mod, c->N);
+  after_launch(c, KID_INNER_PRODUCT, limbs);
 }
 
 void launch_mod_raise(int64_t* res, const int64_t* src, const LimbBatch& batch) {
@@ -312,7 +443,7 @@ void launch_mod_raise(int64_t* res, const int64_t* src, const LimbBatch& batch) 
   Context* c = ctx();
   prof_before(KID_MOD_RAISE);
   mod_raise_kernel<<<grid_for(c->N, 2, batch.count), kThreads, 0, c->stream>>>(
-      U64P(res), CU64P(src), c->primes[0], batch, c->d_mod, c->N);
+      (u64*)res, (const u64*)src, c->primes[0], batch, c->d_mod, c->N);
   after_launch(c, KID_MOD_RAISE, batch.count);
 }
 

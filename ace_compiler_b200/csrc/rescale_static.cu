@@ -85,17 +85,17 @@ extern "C" int Fhert_rescale_static(int64_t* res, const int64_t* poly, size_t le
   const int l = (int)level - 1;
   LimbBatch lb;
   lb.count   = 1;
-  lb.limb[0] = LimbRef{(uint16_t)l, 0, 0, (uint16_t)l};
-  launch_ntt(poly, sc, lb, true);
+  lb.limb[0] = LimbRef{(uint16_t)l, 0, 0, (uint8_t)l, 0};
+  launch_ntt(ptr2(poly), ptr2(sc), lb, true);
   LimbBatch bt;
   bt.count = l;
   for (int i = 0; i < l; i++)
-    bt.limb[i] = LimbRef{(uint16_t)(1 + i), (uint16_t)(1 + i), (uint16_t)(1 + i), (uint16_t)i};
-  launch_rescale_lift(sc, sc, l, bt);
-  launch_ntt(sc, sc, bt, false);
+    bt.limb[i] = LimbRef{(uint16_t)(1 + i), 0, (uint16_t)(1 + i), (uint8_t)i, 0};
+  launch_rescale_lift(ptr2(sc), ptr2(sc), l, bt);
+  launch_ntt(ptr2(sc), ptr2(sc), bt, false);
   for (int i = 0; i < l; i++)
-    bt.limb[i] = LimbRef{(uint16_t)i, (uint16_t)(1 + i), (uint16_t)i, (uint16_t)i};
-  launch_rescale_combine(res, poly, sc, l, bt);
+    bt.limb[i] = LimbRef{(uint16_t)i, (uint16_t)(1 + i), (uint16_t)i, (uint8_t)i, 0};
+  launch_rescale_combine(ptr2(res), ptr2(poly), ptr2(sc), l, bt);
   return FHERT_STATIC_OK;
 }
 

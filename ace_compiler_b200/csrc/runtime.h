@@ -33,23 +33,37 @@ typedef unsigned __int128 u128;
   } while (0)
 
 // Largest number of limbs (Q plus P) a single launch descriptor can carry.
-constexpr int kMaxLimbs = 96;
+constexpr int kMaxLimbs = 192;
 // Largest digit size alpha, and largest number of special primes K.
 constexpr int kMaxDigit = 16;
 
 // One limb of a batched launch: limb offsets (in units of N words) into the
-// base pointers of the launch, and the prime it lives under.
+// base pointers of the launch, the prime it lives under, and which of the two
+// base pointers each operand uses (sel bit 0: a, bit 1: b, bit 2: dst), so
+// that one launch can cover both polynomials of a ciphertext.
 struct LimbRef {
   uint16_t a;      // first operand / source
   uint16_t b;      // second operand
   uint16_t dst;    // result
-  uint16_t prime;  // index into the context's prime list (Q then P)
+  uint8_t  prime;  // index into the context's prime list (Q then P)
+  uint8_t  sel;
 };
 
 struct LimbBatch {
   int     count;
   LimbRef limb[kMaxLimbs];
 };
+
+// Up to two base pointers for one operand of a batched launch.
+struct Ptr2 {
+  u64* p[2];
+};
+inline Ptr2 ptr2(const void* a, const void* b = nullptr) {
+  Ptr2 r;
+  r.p[0] = (u64*)a;
+  r.p[1] = (u64*)b;
+  return r;
+}
 
 // Twiddle entry: root power and its Shoup companion floor(w * 2^64 / q).
 struct __align__(16) Twiddle {
@@ -64,6 +78,7 @@ struct Context {
   int      K     = 0;  // P primes
   int      dnum  = 0;
   int      alpha = 0;  // primes per digit
+  bool     primes_below_2_60 = false;  // enables the carry-free 32-bit-half accumulators
   size_t   q0_bits = 0, sf_bits = 0, hamming_weight = 0, input_level = 0;
   std::vector<u64>     primes;   // L + K
   std::vector<u64>     psi;      // 2N-th root per prime
@@ -123,6 +138,7 @@ enum KernelId {
   KID_NTT_STRIDED, KID_NTT_CONTIG, KID_NTT_SMALL, KID_INTT_STRIDED, KID_INTT_CONTIG,
   KID_INTT_SMALL, KID_ELEMENTWISE, KID_AUTOMORPHISM, KID_MUL_CONST, KID_RESCALE_LIFT,
   KID_RESCALE_COMBINE, KID_BASE_CONV, KID_MODDOWN_COMBINE, KID_INNER_PRODUCT, KID_MOD_RAISE,
+  KID_TENSOR,
   KID_COUNT
 };
 extern const char* const kKernelNames[KID_COUNT];
@@ -151,51 +167,80 @@ uint32_t auto_index_for(Context* c, int32_t rot_idx);
 DevModulus make_dev_modulus(u64 q, uint32_t n);
 
 // ---- kernels (launch wrappers; all queue on ctx()->stream) ----
-// in/out are base pointers; limb.a selects the source limb, limb.dst the result
-void launch_ntt(const int64_t* in, int64_t* out, const LimbBatch& b, bool inverse);
+// limb.a selects the source limb of in.p[sel&1], limb.dst the result limb of
+// out.p[(sel>>2)&1]
+void launch_ntt(Ptr2 in, Ptr2 out, const LimbBatch& b, bool inverse);
 
 enum EwOp { EW_ADD, EW_SUB, EW_MUL, EW_MULADD, EW_ADD_SCALAR, EW_MUL_SCALAR };
 // res[dst] = a[a] op b[b]   (EW_MULADD: res[dst] += a*b; scalar ops ignore b)
-void launch_elementwise(EwOp op, int64_t* res, const int64_t* a, const int64_t* b,
-                        int64_t scalar, const LimbBatch& batch);
+void launch_elementwise(EwOp op, Ptr2 res, Ptr2 a, Ptr2 b, int64_t scalar,
+                        const LimbBatch& batch);
 // res[dst][i] = val[a][table[i]]
-void launch_automorphism(int64_t* res, const int64_t* val, const uint32_t* table,
-                         const LimbBatch& batch);
-// res[dst] = val[a] * c[prime] with per-prime Shoup constants consts[prime]
-void launch_mul_const(int64_t* res, const int64_t* val, const Twiddle* consts,
-                      const LimbBatch& batch);
+void launch_automorphism(Ptr2 res, Ptr2 val, const uint32_t* table, const LimbBatch& batch);
+// res[dst] = val[a] * consts[prime]
+void launch_mul_const(Ptr2 res, Ptr2 val, const Twiddle* consts, const LimbBatch& batch);
+// tensor product of two ciphertexts (evaluator.c:137-173), one launch:
+// d0 = a0*b0, d1 = a0*b1 + a1*b0, d2 = a1*b1 on `level` limbs
+void launch_tensor(int64_t* d0, int64_t* d1, int64_t* d2, const int64_t* a0,
+                   const int64_t* a1, const int64_t* b0, const int64_t* b1, int level);
 
-// Rescale pieces (rns_poly.c:310-404).  `last` = coefficient form of the limb
-// being dropped (prime index l).
-//   lift:    tmp[dst] = switch_modulus(last, q_l -> q_i) * ql_neg[l][i]
+// Rescale pieces (rns_poly.c:310-404).  `last` holds, per selected base, the
+// coefficient form of the limb being dropped (prime index l) at limb.b.
+//   lift:    tmp[dst] = switch_modulus(last[b], q_l -> q_i) * ql_neg[l][i]
 //   combine: res[dst] = poly[a] * ql_inv[l][i] + tmp[b]
-void launch_rescale_lift(int64_t* tmp, const int64_t* last, int l, const LimbBatch& batch);
-void launch_rescale_combine(int64_t* res, const int64_t* poly, const int64_t* tmp, int l,
-                            const LimbBatch& batch);
+void launch_rescale_lift(Ptr2 tmp, Ptr2 last, int l, const LimbBatch& batch);
+void launch_rescale_combine(Ptr2 res, Ptr2 poly, Ptr2 tmp, int l, const LimbBatch& batch);
 
-// Approximate base conversion (rns_poly.c:218-242, rns_poly_impl.c:287-339):
-//   y_i = in[i] * inv[i] mod p_in(i);  out[o] = (sum_i y_i * mat(i,o)) mod p_out(o)
-// mat(i,o) = mat[i*in_stride + out.limb[o].b*out_stride]; in.limb[i].a addresses the
-// source limb, out.limb[o].dst the result limb.
-void launch_base_conv(int64_t* out, const int64_t* in, const LimbBatch& in_limbs,
-                      const LimbBatch& out_limbs, const Twiddle* inv, const u64* mat,
-                      int in_stride, int out_stride);
-// ModDown tail: res[dst] = (x[a] - t[b]) * P^-1 mod q_i
-void launch_moddown_combine(int64_t* res, const int64_t* x, const int64_t* t,
-                            const LimbBatch& batch);
-
-// Key inner product over `parts` digits: for every limb of the batch
-//   acc0[dst] = sum_j ext_j[a] * key0_j[b],  acc1[dst] = sum_j ext_j[a] * key1_j[b]
-// acc1/key1 may be null (single product).
+// Approximate base conversion (rns_poly.c:218-242, rns_poly_impl.c:287-339) of
+// up to kMaxParts independent groups in one launch:
+//   y_i = in[first_limb+i] * inv[i] mod p(first_prime+i)
+//   out[limb(m)] = (sum_i y_i * mat[i*in_stride + prime(m)*out_stride]) mod prime(m)
+// for every m in [0, out_total) outside [skip_start, skip_start+skip_len), where
+// prime(m) = m < level ? m : L + m - level and limb(m) = m < level ? m : p_limb + m - level.
 constexpr int kMaxParts = 16;
+struct ConvGroup {
+  const u64*     in;
+  u64*           out;
+  const Twiddle* inv;
+  const u64*     mat;
+  int            first_limb, first_prime, count;
+  int            skip_start, skip_len;
+};
+struct ConvArgs {
+  int       groups, level, out_total, p_limb, in_stride, out_stride;
+  ConvGroup g[kMaxParts];
+};
+void launch_base_conv(const ConvArgs& args);
+
+// ModDown tail for up to two polynomials:
+//   res[g][i] = (x[g][i] - t[g][i]) * P^-1 mod q_i (+ add[g][i] when add[g] is set)
+struct ModDownTail {
+  int        polys, level;
+  u64*       res[2];
+  const u64* x[2];
+  const u64* t[2];
+  const u64* add[2];
+};
+void launch_moddown_combine(const ModDownTail& args);
+
+// Key inner product over `parts` digits for limbs m in [0, level+K):
+//   e_j = (in and m < level and m / alpha == j) ? in[m] : ext_ptr[j][m]
+//   acc0[m] = sum_j e_j * key0_j[prime(m)],  acc1[m] = sum_j e_j * key1_j[prime(m)]
+// acc/ext use level Q limbs followed directly by K P limbs; keys have their P
+// limbs at limb index key_p_limb.  in may be null (ext then holds every limb);
+// acc1/key1 may be null (single product).
 struct InnerArgs {
-  int        parts;
-  const u64* ext[kMaxParts];
+  int        parts, level, alpha, key_p_limb;
+  const u64* in;
+  const u64* ext_ptr[kMaxParts];
   const u64* key0[kMaxParts];
   const u64* key1[kMaxParts];
+  u64*       acc0;
+  u64*       acc1;
+  int        acc_p_limb;  // limb index of the first P limb in acc
+  int        ext_p_limb;  // limb index of the first P limb in ext
 };
-void launch_inner_product(int64_t* acc0, int64_t* acc1, const InnerArgs& args,
-                          const LimbBatch& batch);
+void launch_inner_product(const InnerArgs& args);
 // Mod-raise (rns_poly.c:1101-1125): res[dst] = switch_modulus(src, q_0 -> q_i)
 void launch_mod_raise(int64_t* res, const int64_t* src, const LimbBatch& batch);
 

@@ -226,3 +226,33 @@ def test_mul_relin_rescale(pair):
         assert res._sf_degree == 1
         for c in (ca, cb, prod, res):
             gpu.free_ciph(c)
+
+
+def test_extreme_residues_through_base_conversion(pair):
+    """every residue at its maximum q-1: the worst case for the lazy
+    accumulators of ModUp, ModDown and the key inner product"""
+    import ace_compiler_b200 as rt
+    ref, gpu, rots = pair
+    level = gpu.L
+    top = np.stack([np.full(gpu.N, p - 1, np.int64) for p in gpu.primes])
+    src = gpu.new_poly(level, data=top[:level])
+    for part in range(ref.num_decomp(level)):
+        ext = gpu.new_poly(level, extended=True)
+        gpu.lib.Decomp_modup(ext, src, part)
+        assert np.array_equal(gpu.download(ext), ref.decomp_modup(top[:level], part))
+        gpu.free(ext)
+    gpu.free(src)
+    ext = gpu.new_poly(level, extended=True, data=top)
+    out = gpu.new_poly(level)
+    gpu.lib.Mod_down(out, ext)
+    assert np.array_equal(gpu.download(out), ref.mod_down(top, level))
+    gpu.free(ext)
+    gpu.free(out)
+    ct = gpu.new_ciph(top[:level], top[:level])
+    res = rt.CIPHERTEXT()
+    gpu.lib.Rotate_ciph(C.byref(res), C.byref(ct), rots[0])
+    g0, g1 = gpu.ciph_to_host(res)
+    e0, e1 = ref.rotate(top[:level], top[:level], rots[0])
+    assert np.array_equal(g0, e0) and np.array_equal(g1, e1)
+    gpu.free_ciph(ct)
+    gpu.free_ciph(res)
