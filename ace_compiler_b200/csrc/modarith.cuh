@@ -99,13 +99,22 @@ struct Acc4 {
 
 __device__ __forceinline__ void acc4_zero(Acc4& c) { c.s00 = c.s01 = c.s10 = c.s11 = 0; }
 
+// acc += a * b as one 32x32+64 multiply-add
+__device__ __forceinline__ void mad_wide(u64& acc, uint32_t a, uint32_t b) {
+  asm("mad.wide.u32 %0, %1, %2, %0;" : "+l"(acc) : "r"(a), "r"(b));
+}
+
+__device__ __forceinline__ void acc4_mac_halves(Acc4& c, uint32_t a0, uint32_t a1, uint32_t b0,
+                                                uint32_t b1) {
+  mad_wide(c.s00, a0, b0);
+  mad_wide(c.s01, a0, b1);
+  mad_wide(c.s10, a1, b0);
+  mad_wide(c.s11, a1, b1);
+}
+
 __device__ __forceinline__ void acc4_mac(Acc4& c, u64 a, u64 b) {
-  uint32_t a0 = (uint32_t)a & 0x3fffffffu, a1 = (uint32_t)(a >> 30);
-  uint32_t b0 = (uint32_t)b & 0x3fffffffu, b1 = (uint32_t)(b >> 30);
-  c.s00 += (u64)a0 * b0;
-  c.s01 += (u64)a0 * b1;
-  c.s10 += (u64)a1 * b0;
-  c.s11 += (u64)a1 * b1;
+  acc4_mac_halves(c, (uint32_t)a & 0x3fffffffu, (uint32_t)(a >> 30),
+                  (uint32_t)b & 0x3fffffffu, (uint32_t)(b >> 30));
 }
 
 __device__ __forceinline__ void acc4_add_shifted(u64& hi, u64& lo, u64 v, int sh) {

@@ -147,10 +147,11 @@ template <int NIN, bool FAST>
 __global__ void __launch_bounds__(kThreads)
 base_conv_kernel(ConvArgs args, int chunk, int num_q, const DevModulus* __restrict__ mods,
                  uint32_t n) {
-  __shared__ u64  sm_mat[kMaxOutChunk * NIN];
-  const ConvGroup g         = args.g[blockIdx.z];
-  const int       out_count = args.out_total - g.skip_len;
-  const int       o_beg     = blockIdx.y * chunk;
+  // FAST keeps the matrix pre-split into 30-bit halves (x = low, y = high)
+  __shared__ uint2 sm_mat[kMaxOutChunk * NIN];
+  const ConvGroup  g         = args.g[blockIdx.z];
+  const int        out_count = args.out_total - g.skip_len;
+  const int        o_beg     = blockIdx.y * chunk;
   if (o_beg >= out_count) return;
   const int o_end = min(o_beg + chunk, out_count);
   for (int t = threadIdx.x; t < (o_end - o_beg) * NIN; t += kThreads) {
@@ -158,41 +159,50 @@ base_conv_kernel(ConvArgs args, int chunk, int num_q, const DevModulus* __restri
     int m = o_beg + o;
     m     = m < g.skip_start ? m : m + g.skip_len;
     int prime = m < args.level ? m : num_q + (m - args.level);
-    sm_mat[t] = i < g.count
-                    ? g.mat[(size_t)i * args.in_stride + (size_t)prime * args.out_stride]
-                    : 0;
+    u64 v = i < g.count
+                ? g.mat[(size_t)i * args.in_stride + (size_t)prime * args.out_stride]
+                : 0;
+    sm_mat[t] = FAST ? make_uint2((uint32_t)v & 0x3fffffffu, (uint32_t)(v >> 30))
+                     : make_uint2((uint32_t)v, (uint32_t)(v >> 32));
   }
   __syncthreads();
   const uint32_t c = blockIdx.x * kThreads + threadIdx.x;
   if (c >= n) return;
-  u64 y[NIN];
+  uint32_t y0[NIN], y1[NIN];  // halves of y_i: 30-bit split (FAST) or 32-bit split
 #pragma unroll
   for (int i = 0; i < NIN; i++) {
+    u64 y = 0;
     if (i < g.count) {
       const Twiddle w = g.inv[i];
-      y[i] = mul_shoup(g.in[(size_t)(g.first_limb + i) * n + c], w.w, w.wp,
-                       mods[g.first_prime + i].q);
-    } else {
-      y[i] = 0;
+      y = mul_shoup(g.in[(size_t)(g.first_limb + i) * n + c], w.w, w.wp,
+                    mods[g.first_prime + i].q);
     }
+    y0[i] = FAST ? ((uint32_t)y & 0x3fffffffu) : (uint32_t)y;
+    y1[i] = FAST ? (uint32_t)(y >> 30) : (uint32_t)(y >> 32);
   }
   for (int o = o_beg; o < o_end; o++) {
     int m     = o < g.skip_start ? o : o + g.skip_len;
     int prime = m < args.level ? m : num_q + (m - args.level);
     int limb  = m < args.level ? m : args.p_limb + (m - args.level);
     const DevModulus md  = mods[prime];
-    const u64*       row = sm_mat + (o - o_beg) * NIN;
+    const uint2*     row = sm_mat + (o - o_beg) * NIN;
     u64              hi, lo;
     if (FAST) {
       Acc4 acc;
       acc4_zero(acc);
 #pragma unroll
-      for (int i = 0; i < NIN; i++) acc4_mac(acc, y[i], row[i]);
+      for (int i = 0; i < NIN; i++) {
+        const uint2 b = row[i];
+        acc4_mac_halves(acc, y0[i], y1[i], b.x, b.y);
+      }
       acc4_fold(acc, hi, lo);
     } else {
       hi = lo = 0;
 #pragma unroll
-      for (int i = 0; i < NIN; i++) mac_128(hi, lo, y[i], row[i]);
+      for (int i = 0; i < NIN; i++) {
+        const uint2 b = row[i];
+        mac_128(hi, lo, ((u64)y1[i] << 32) | y0[i], ((u64)b.y << 32) | b.x);
+      }
     }
     g.out[(size_t)limb * n + c] = reduce_128(hi, lo, md);
   }
