@@ -48,6 +48,15 @@ class CIPHERTEXT3(C.Structure):
     ]
 
 
+class PLAINTEXT(C.Structure):
+    _fields_ = [
+        ("_poly", POLYNOMIAL),
+        ("_slots", C.c_uint32),
+        ("_scaling_factor", C.c_double),
+        ("_sf_degree", C.c_uint32),
+    ]
+
+
 class MODULUS(C.Structure):
     _fields_ = [
         ("_val", C.c_int64),
@@ -62,6 +71,7 @@ class MODULUS(C.Structure):
 POLY = C.POINTER(POLYNOMIAL)
 CIPHER = C.POINTER(CIPHERTEXT)
 CIPHER3 = C.POINTER(CIPHERTEXT3)
+PLAIN = C.POINTER(PLAINTEXT)
 MODP = C.POINTER(MODULUS)
 I64P = C.c_void_p  # device or host int64 buffers travel as raw addresses
 
@@ -130,6 +140,19 @@ SIGNATURES = {
     "Set_pk0": (None, [POLY, C.c_void_p, C.c_uint32]),
     "Set_pk1": (None, [POLY, C.c_void_p, C.c_uint32]),
     "Fhert_import_switch_key": (None, [C.c_bool, C.c_int32, C.c_uint32, C.c_int, C.c_void_p]),
+    "Fhert_seed": (None, [C.c_void_p, C.c_uint64, C.c_int64]),
+    "Encode_float": (None, [PLAIN, C.c_void_p, C.c_size_t, C.c_uint32, C.c_uint32]),
+    "Encode_double": (None, [PLAIN, C.c_void_p, C.c_size_t, C.c_uint32, C.c_uint32]),
+    "Encode_float_mask": (None, [PLAIN, C.c_float, C.c_size_t, C.c_uint32, C.c_uint32]),
+    "Encode_double_mask": (None, [PLAIN, C.c_double, C.c_size_t, C.c_uint32, C.c_uint32]),
+    "Encode_dcmplx": (None, [PLAIN, C.c_void_p, C.c_size_t, C.c_uint32, C.c_uint32]),
+    "Free_plain_data": (None, [PLAIN]),
+    "Encrypt": (CIPHER, [CIPHER, PLAIN]),
+    "Fhert_decrypt": (None, [PLAIN, CIPHER]),
+    "Fhert_decode": (None, [PLAIN, C.c_void_p, C.c_size_t]),
+    "Get_msg": (C.c_void_p, [CIPHER]),
+    "Fhert_export_switch_key": (None, [C.c_bool, C.c_int32, C.c_uint32, C.c_int, C.c_void_p]),
+    "Fhert_export_key": (None, [C.c_int, C.c_void_p]),
     "Init_ciph_same_scale": (None, [CIPHER, CIPHER, CIPHER]),
     "Init_ciph_up_scale": (None, [CIPHER, CIPHER, CIPHER]),
     "Init_ciph_down_scale": (None, [CIPHER, CIPHER]),
@@ -181,8 +204,15 @@ class Runtime:
     """
 
     def __init__(self, degree, num_q, q0_bits=60, sf_bits=56, num_q_parts=3, input_level=0,
-                 hamming_weight=192, rot_idxs=()):
+                 hamming_weight=192, rot_idxs=(), keygen=False, seed=None, fake_time_us=-1):
+        """keygen=False skips key generation (switch keys are then imported);
+        seed = 16 uint32 words pins the sample generator as Fhert_seed does."""
         self.lib = load()
+        os.environ["FHERT_SKIP_KEYGEN"] = "0" if keygen else "1"
+        if seed is not None:
+            s = np.ascontiguousarray(seed, dtype=np.uint32)
+            assert s.shape == (16,)
+            self.lib.Fhert_seed(_ptr(s), 0, fake_time_us)
         rot = (C.c_int32 * max(1, len(rot_idxs)))(*rot_idxs)
         self.lib.Fhert_set_context_params(degree, num_q, q0_bits, sf_bits, num_q_parts,
                                           input_level, hamming_weight, len(rot_idxs), rot)
@@ -278,6 +308,45 @@ class Runtime:
 
     def free_ciph(self, ct):
         self.lib.Free_ciph_poly(C.byref(ct), 1)
+
+    # --- client side -------------------------------------------------------
+    def encode(self, values, sf_degree=1, level=0):
+        """Complex (or real) slot values -> PLAINTEXT in NTT form on the device."""
+        v = np.ascontiguousarray(np.asarray(values, dtype=np.complex128))
+        pt = PLAINTEXT()
+        self.lib.Encode_dcmplx(C.byref(pt), _ptr(v.view(np.float64)), len(v), sf_degree, level)
+        return pt
+
+    def encode_scalar(self, value, sf_degree=1, level=0):
+        pt = PLAINTEXT()
+        d = C.c_double(value)
+        self.lib.Encode_double(C.byref(pt), C.byref(d), 1, sf_degree, level)
+        return pt
+
+    def encrypt(self, pt):
+        ct = CIPHERTEXT()
+        self.lib.Encrypt(C.byref(ct), C.byref(pt))
+        return ct
+
+    def decrypt_decode(self, ct, count=None):
+        count = count or self.N // 2
+        pt = PLAINTEXT()
+        self.lib.Fhert_decrypt(C.byref(pt), C.byref(ct))
+        out = np.zeros(count, np.complex128)
+        self.lib.Fhert_decode(C.byref(pt), _ptr(out.view(np.float64)), count)
+        self.lib.Free_plain_data(C.byref(pt))
+        return out
+
+    def export_key(self, which):
+        limbs = self.L + self.K if which < 2 else self.L
+        out = np.zeros((limbs, self.N), np.int64)
+        self.lib.Fhert_export_key(which, _ptr(out))
+        return out
+
+    def export_switch_key(self, is_rot, rot_idx, part, which):
+        out = np.zeros((self.L + self.K, self.N), np.int64)
+        self.lib.Fhert_export_switch_key(is_rot, rot_idx, part, which, _ptr(out))
+        return out
 
     def import_switch_key(self, is_rot, rot_idx, part, which, data):
         data = np.ascontiguousarray(data, dtype=np.int64)

@@ -112,6 +112,8 @@ void Prepare_context(void) {
   FHERT_ASSERT(p != nullptr, "Get_context_params returned no parameters");
   Context* c = create_context(p);
   for (size_t i = 0; i < p->_num_rot_idx; i++) auto_index_for(c, p->_rot_idxs[i]);
+  const char* skip = std::getenv("FHERT_SKIP_KEYGEN");
+  if (!(skip != nullptr && skip[0] != '\0' && skip[0] != '0')) generate_keys(c);
   std::printf(
       "ckks_param: _provider = %d, _poly_degree = %d, mul_depth = %ld, input_lev = %ld, "
       "_first_mod_size = %ld, _scaling_mod_size = %ld, _num_q_parts = %ld, _num_p = %ld, "
@@ -325,15 +327,25 @@ POLY Conv_ntt2poly_inplace(POLY poly) {
 }
 
 static POLY binary_poly(EwOp op, POLY res, POLY a, POLY b) {
-  Context* c     = ctx();
-  size_t   level = res->_num_primes;
+  Context* c = ctx();
+  // operands in coefficient form are brought to NTT form in place, as the CPU
+  // runtime does: always for a product, only on a mismatch for sums
+  // (rns_poly.c:852-858, 900-906, 950-956)
+  if (op == EW_MUL) {
+    if (!a->_is_ntt) Conv_poly2ntt_inplace(a);
+    if (!b->_is_ntt) Conv_poly2ntt_inplace(b);
+  } else if (a->_is_ntt != b->_is_ntt) {
+    if (!a->_is_ntt) Conv_poly2ntt_inplace(a);
+    else Conv_poly2ntt_inplace(b);
+  }
+  size_t level = res->_num_primes;
   FHERT_ASSERT(level <= a->_num_primes && level <= b->_num_primes, "operand level too low");
   size_t num_p = res->_num_primes_p;
   FHERT_ASSERT(num_p == 0 || (a->_num_primes_p == num_p && b->_num_primes_p == num_p),
                "unmatched special limbs");
   launch_elementwise(op, ptr2(res->_data), ptr2(a->_data), ptr2(b->_data), 0,
                      poly_batch(c, res, a, b, level, num_p));
-  res->_is_ntt = a->_is_ntt;
+  res->_is_ntt = op == EW_MUL ? true : a->_is_ntt;
   return res;
 }
 
@@ -671,29 +683,6 @@ int64_t* Auto_order(int32_t rot_idx) {
   Context* c = ctx();
   uint32_t k = (rot_idx == (int32_t)(2 * c->N - 1)) ? (uint32_t)rot_idx : auto_index_for(c, rot_idx);
   return reinterpret_cast<int64_t*>(auto_table(c, k));
-}
-
-static SWITCH_KEY* key_slot(Context* c, uint32_t key_id, bool create) {
-  auto it = c->keys.find(key_id);
-  if (it != c->keys.end()) return it->second;
-  if (!create) return nullptr;
-  SWITCH_KEY* k = new SWITCH_KEY();
-  k->_num_parts = c->dnum;
-  k->_parts     = new PUBLIC_KEY[c->dnum];
-  std::memset(k->_parts, 0, sizeof(PUBLIC_KEY) * c->dnum);
-  size_t words = (size_t)(c->L + c->K) * c->N;
-  for (int j = 0; j < c->dnum; j++) {
-    for (POLYNOMIAL* p : {&k->_parts[j]._p0, &k->_parts[j]._p1}) {
-      p->_ring_degree      = c->N;
-      p->_num_primes       = c->L;
-      p->_num_primes_p     = c->K;
-      p->_num_alloc_primes = c->L + c->K;
-      p->_is_ntt           = true;
-      CUDA_CHECK(cudaMalloc(&p->_data, words * sizeof(int64_t)));
-    }
-  }
-  c->keys[key_id] = k;
-  return k;
 }
 
 static uint32_t key_id_for(Context* c, bool is_rot, int32_t rot_idx) {

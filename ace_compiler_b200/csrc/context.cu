@@ -161,12 +161,50 @@ static u64 find_generator(u64 q) {
   return 0;
 }
 
-// util/src/number_theory.c:141-162 (table look-up in std_param.c:229 holds no
-// entry for the ring degrees served here, so the generator path is taken)
+// The CPU runtime keeps a table of 2N-th roots for the prime chains of two ring
+// degrees (util/src/std_param.c:229-300, orders 32 and 32768); every entry is
+// the smallest primitive root of that order, and the primes covered are the
+// first few lattice primes (= 1 mod order) below and above 2^60, 2^59 and 2^50.
+// This reproduces which primes the table covers.
+static bool root_table_covers(u64 order, u64 q) {
+  struct Span { u64 order; int bits, below, above; };
+  static const Span spans[] = {{32, 60, 9, 0},     {32, 59, 10, 11},    {32, 50, 2, 3},
+                               {32768, 60, 10, 0}, {32768, 59, 12, 13}};
+  for (const Span& s : spans) {
+    if (s.order != order) continue;
+    u64 c = (1ull << s.bits) + 1;
+    for (int found = 0; found < s.below;) {
+      c -= order;
+      if (is_prime(c)) {
+        if (c == q) return true;
+        found++;
+      }
+    }
+    c = (1ull << s.bits) + 1;
+    for (int found = 0; found < s.above;) {
+      c += order;
+      if (is_prime(c)) {
+        if (c == q) return true;
+        found++;
+      }
+    }
+  }
+  return false;
+}
+
+// util/src/number_theory.c:141-162: table value when the table covers the prime,
+// else generator^((q-1)/order) with the smallest generator
 static u64 root_of_unity(u64 order, u64 q) {
   FHERT_ASSERT((q - 1) % order == 0, "modulus-1 not divisible by order");
-  u64 g = find_generator(q);
-  return powmod(g, (q - 1) / order, q);
+  u64 g    = find_generator(q);
+  u64 root = powmod(g, (q - 1) / order, q);
+  if (!root_table_covers(order, q)) return root;
+  u64 sq = mulmod(root, root, q), cur = root, best = root;
+  for (u64 k = 0; k < order / 2; k++) {  // all odd powers of root
+    if (cur < best) best = cur;
+    cur = mulmod(cur, sq, q);
+  }
+  return best;
 }
 
 static uint32_t bit_reverse(uint32_t v, int bits) {
@@ -465,6 +503,8 @@ Context* create_context(const CKKS_PARAMS* p) {
 void destroy_context() {
   Context* c = g_ctx;
   if (!c) return;
+  free_keys(c);
+  release_prng();
   cudaStreamSynchronize(c->stream);
   cudaFree(c->d_mod);
   cudaFree(c->d_fwd);

@@ -124,6 +124,13 @@ struct Context {
   std::map<int32_t, uint32_t> auto_idx;
   // keys by automorphism index; 0 = relinearisation key
   std::map<uint32_t, SWITCH_KEY*> keys;
+  // secret key in coefficient and NTT form (L Q limbs + K P limbs), public key
+  // (L limbs); empty until generate_keys ran
+  POLYNOMIAL sk_s{}, sk_ntt{};
+  PUBLIC_KEY pk{};
+  // encoder tables (util/src/ntt.c:562-590): 2N-th complex roots, powers of 5
+  std::vector<double>   fft_rou_re, fft_rou_im;
+  std::vector<uint32_t> fft_rot_group;
 
   cudaStream_t stream = nullptr;
   uint64_t     launches = 0;
@@ -159,6 +166,24 @@ bool is_prime(u64 n);
 u64  shoup(u64 w, u64 q);
 const Context::ModUpTable& modup_table(Context* c, int level, int digit);
 uint32_t* auto_table(Context* c, uint32_t k);
+
+// ---- sampling.cu (host randomness, same generators as the CPU runtime) ----
+void seed_prng(const uint32_t seed[16], u64 counter, int64_t fake_time_us);
+void release_prng();
+void sample_uniform(int64_t* out, size_t n, u64 upper_bound);
+void sample_ternary(int64_t* out, size_t n, size_t hamming_weight);
+void sample_triangle(int64_t* out, size_t n);
+
+// ---- client.cu ----
+void generate_keys(Context* c);
+void free_keys(Context* c);
+SWITCH_KEY* key_slot(Context* c, uint32_t key_id, bool create);
+// msg[N] (signed values, negatives stored as Max64 + x) -> residues per limb,
+// times scale_pow[prime] when given                       (crt.c:1153-1221)
+void launch_encode_split(int64_t* poly, const int64_t* msg, const u64* scale_pow,
+                         const LimbBatch& batch);
+// small signed samples (-1, 0, 1) -> residues per limb (crt.c:1168-1172)
+void launch_small_to_rns(int64_t* poly, const int64_t* vals, const LimbBatch& batch);
 
 // ---- context.cu ----
 Context* create_context(const CKKS_PARAMS* p);

@@ -129,8 +129,10 @@ void Fhert_set_context_params(uint32_t degree, size_t num_q, size_t q0_bits,
 
 /* Prepare_context builds the prime chain, the NTT and base-conversion tables
  * (same primes, roots and constants as ckks_context.c:84 -> crt.c:607) and
- * uploads them.  Keys are generated unless FHERT_SKIP_KEYGEN=1 is set, in
- * which case they are supplied with Fhert_import_switch_key. */
+ * uploads them, then generates secret, public, relinearisation and rotation
+ * keys in the CPU runtime's order (ant/ckks/src/key_gen.c:15-38) unless the
+ * environment variable FHERT_SKIP_KEYGEN=1 is set, in which case switch keys
+ * are supplied with Fhert_import_switch_key. */
 void     Prepare_context(void);
 void     Finalize_context(void);
 uint32_t Degree(void);         /* ckks_context.c:163 */
@@ -256,6 +258,43 @@ void     Set_pk1(POLY pk, SW_KEY swk, uint32_t part);
  * limbs followed by K P limbs in NTT form. */
 void Fhert_import_switch_key(bool is_rot, int32_t rot_idx, uint32_t part,
                              int which, const int64_t* host);
+
+/* ------------------------------------------------------------------------ */
+/* Client side: seeding, encode, encrypt, decrypt, decode                   */
+/* ------------------------------------------------------------------------ */
+
+/* Installs the 16-word key and the counter of the BLAKE2Xb generator that
+ * uniform and ternary samples come from (ant/util/src/prng.c:13-93) and, when
+ * fake_time_us >= 0, the clock value that seeds libc rand() for the triangle
+ * error samples (ant/util/src/random_sample.c:25-29).  With the same three
+ * values the CPU runtime produces the same keys and ciphertexts.  Without this
+ * call the generator seeds itself from the clock and /dev/urandom as the CPU
+ * runtime does.  Call before Prepare_context. */
+void Fhert_seed(const uint32_t seed[16], uint64_t counter, int64_t fake_time_us);
+
+/* ant/ckks/src/plain.c:29-102 -> encoder.c:234-325 (vectors: inverse canonical
+ * embedding on the host, scaling, rounding, RNS split and NTT on the device) and
+ * encoder.c:473-575 (len == 1: one scalar on every coefficient) */
+void Encode_float(PLAIN plain, float* input, size_t len, uint32_t sc_degree, uint32_t level);
+void Encode_double(PLAIN plain, double* input, size_t len, uint32_t sc_degree, uint32_t level);
+void Encode_float_mask(PLAIN plain, float cst, size_t len, uint32_t sc_degree, uint32_t level);
+void Encode_double_mask(PLAIN plain, double cst, size_t len, uint32_t sc_degree, uint32_t level);
+/* input = len (re, im) pairs */
+void Encode_dcmplx(PLAIN plain, double* re_im, size_t len, uint32_t sc_degree, uint32_t level);
+void Free_plain_data(PLAIN plain);
+
+CIPHER  Encrypt(CIPHER res, PLAIN plain);     /* ant/ckks/src/encryptor.c:19 */
+void    Fhert_decrypt(PLAIN res, CIPHER ciph); /* ant/ckks/src/decryptor.c:19 */
+/* ant/ckks/src/encoder.c:657: writes `count` (re, im) pairs */
+void    Fhert_decode(PLAIN plain, double* out, size_t count);
+double* Get_msg(CIPHER ciph);                 /* ant/ckks/src/cipher.c Get_msg */
+
+/* key material as host residues: switch-key polynomials hold L Q limbs then K
+ * P limbs; Fhert_export_key: 0 = secret key (coefficient form, L+K limbs),
+ * 1 = secret key in NTT form, 2 / 3 = public key polynomials (L limbs) */
+void Fhert_export_switch_key(bool is_rot, int32_t rot_idx, uint32_t part, int which,
+                             int64_t* host);
+void Fhert_export_key(int which, int64_t* host);
 
 /* ------------------------------------------------------------------------ */
 /* Ciphertext level  (ant/ckks/src/cipher.c, evaluator.c)                    */

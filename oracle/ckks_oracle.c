@@ -150,10 +150,45 @@ u64 Oracle_find_generator(u64 q) {
   return 0;
 }
 
-/* util/src/number_theory.c:141-162 without the fixed table of std_param.c:229
- * (which only lists ring degrees 16 and 16384 for a particular prime set) */
+/* util/src/std_param.c:229-300: the reference tabulates 2N-th roots for the
+ * prime chains of ring degrees 16 and 16384; each entry is the smallest
+ * primitive root of that order and the covered primes are the first lattice
+ * primes (1 mod order) below / above 2^60, 2^59 and 2^50. */
+static int Root_table_covers(u64 order, u64 q) {
+  static const struct { u64 order; int bits, below, above; } spans[] = {
+      {32, 60, 9, 0}, {32, 59, 10, 11}, {32, 50, 2, 3}, {32768, 60, 10, 0}, {32768, 59, 12, 13}};
+  for (int s = 0; s < 5; s++) {
+    if (spans[s].order != order) continue;
+    u64 c = (1ull << spans[s].bits) + 1;
+    for (int found = 0; found < spans[s].below;) {
+      c -= order;
+      if (Oracle_is_prime(c)) {
+        if (c == q) return 1;
+        found++;
+      }
+    }
+    c = (1ull << spans[s].bits) + 1;
+    for (int found = 0; found < spans[s].above;) {
+      c += order;
+      if (Oracle_is_prime(c)) {
+        if (c == q) return 1;
+        found++;
+      }
+    }
+  }
+  return 0;
+}
+
+/* util/src/number_theory.c:141-162 */
 u64 Oracle_root_of_unity(u64 order, u64 q) {
-  return Oracle_pow_mod(Oracle_find_generator(q), (q - 1) / order, q);
+  u64 root = Oracle_pow_mod(Oracle_find_generator(q), (q - 1) / order, q);
+  if (!Root_table_covers(order, q)) return root;
+  u64 sq = Mul_mod(root, root, q), cur = root, best = root;
+  for (u64 k = 0; k < order / 2; k++) {
+    if (cur < best) best = cur;
+    cur = Mul_mod(cur, sq, q);
+  }
+  return best;
 }
 
 static uint32_t Brv(uint32_t v, int bits) {

@@ -12,6 +12,8 @@
  * Buffers are limb-major: limb i occupies [i*N, (i+1)*N).  "Extended" buffers
  * hold `level` Q limbs followed directly by K special (P) limbs.
  */
+#include <complex.h>
+#include <math.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -242,4 +244,90 @@ void Ref_relinearize(const int64_t* c0, const int64_t* c1, const int64_t* c2,
   Export_ciph(&res, out0, out1);
   Free_poly_data(Get_c0(&res));
   Free_poly_data(Get_c1(&res));
+}
+
+/* ---- client side: keys, encode, encrypt, decrypt, decode ---- */
+
+//! which: 0 secret key (coefficient form, L+K limbs), 1 secret key NTT form,
+//! 2 / 3 public key polynomials (L limbs)
+void Ref_export_key(int which, int64_t* out) {
+  CKKS_KEY_GENERATOR* gen = (CKKS_KEY_GENERATOR*)Keygen();
+  POLY                p   = which == 0   ? Get_sk_poly(gen->_secret_key)
+                            : which == 1 ? Get_ntt_sk(gen->_secret_key)
+                            : which == 2 ? Get_pk0(gen->_public_key)
+                                         : Get_pk1(gen->_public_key);
+  size_t              n   = Degree();
+  memcpy(out, Get_poly_coeffs(p), Poly_level(p) * n * sizeof(int64_t));
+  if (Num_p(p)) {
+    memcpy(out + Poly_level(p) * n, Get_p_coeffs(p), Num_p(p) * n * sizeof(int64_t));
+  }
+}
+
+//! values = len (re, im) pairs; out = level limbs in NTT form
+void Ref_encode(const double* values, size_t len, uint32_t sf_degree, uint32_t level,
+                int64_t* out) {
+  VALUE_LIST* vec = Alloc_value_list(DCMPLX_TYPE, len);
+  for (size_t i = 0; i < len; i++) {
+    DCMPLX_VALUE_AT(vec, i) = values[2 * i] + values[2 * i + 1] * I;
+  }
+  PLAINTEXT plain;
+  memset(&plain, 0, sizeof(plain));
+  Encode_at_level_with_sf(&plain, (CKKS_ENCODER*)Encoder(), vec, level, 0, sf_degree);
+  POLY p = Get_plain_poly(&plain);
+  memcpy(out, Get_poly_coeffs(p), Poly_level(p) * Degree() * sizeof(int64_t));
+  Free_poly_data(p);
+  Free_value_list(vec);
+}
+
+//! scalar path of Encode_double (len == 1)
+void Ref_encode_scalar(double value, uint32_t sf_degree, uint32_t level, int64_t* out) {
+  PLAINTEXT plain;
+  memset(&plain, 0, sizeof(plain));
+  Encode_val_at_level(&plain, (CKKS_ENCODER*)Encoder(), value, level, sf_degree);
+  POLY p = Get_plain_poly(&plain);
+  memcpy(out, Get_poly_coeffs(p), Poly_level(p) * Degree() * sizeof(int64_t));
+  Free_poly_data(p);
+}
+
+//! encrypts a plaintext polynomial (level limbs, NTT form)
+void Ref_encrypt(const int64_t* plain_poly, size_t level, uint32_t sf_degree, int64_t* c0,
+                 int64_t* c1) {
+  PLAINTEXT  plain;
+  CIPHERTEXT ciph;
+  memset(&plain, 0, sizeof(plain));
+  memset(&ciph, 0, sizeof(ciph));
+  Wrap_poly(&plain._poly, (int64_t*)plain_poly, level, 0, 1);
+  plain._slots          = Degree() / 2;
+  plain._scaling_factor = pow(Get_default_sc(), sf_degree);
+  plain._sf_degree      = sf_degree;
+  Encrypt_msg(&ciph, (CKKS_ENCRYPTOR*)Encryptor(), &plain);
+  Export_ciph(&ciph, c0, c1);
+  Free_poly_data(Get_c0(&ciph));
+  Free_poly_data(Get_c1(&ciph));
+}
+
+//! decrypts and decodes; out = count (re, im) pairs
+void Ref_decrypt_decode(const int64_t* c0, const int64_t* c1, size_t level, uint32_t sf_degree,
+                        double* out, size_t count) {
+  size_t     n     = Degree();
+  size_t     bytes = level * n * sizeof(int64_t);
+  int64_t*   t0    = (int64_t*)malloc(bytes);
+  int64_t*   t1    = (int64_t*)malloc(bytes);
+  CIPHERTEXT ciph;
+  PLAINTEXT  plain;
+  memcpy(t0, c0, bytes);
+  memcpy(t1, c1, bytes);
+  Wrap_ciph(&ciph, t0, t1, level, pow(Get_default_sc(), sf_degree), sf_degree);
+  memset(&plain, 0, sizeof(plain));
+  Decrypt(&plain, (CKKS_DECRYPTOR*)Decryptor(), &ciph, NULL);
+  VALUE_LIST* res = Alloc_value_list(DCMPLX_TYPE, count);
+  Decode(res, (CKKS_ENCODER*)Encoder(), &plain);
+  for (size_t i = 0; i < count; i++) {
+    out[2 * i]     = creal(DCMPLX_VALUE_AT(res, i));
+    out[2 * i + 1] = cimag(DCMPLX_VALUE_AT(res, i));
+  }
+  Free_value_list(res);
+  Free_poly_data(Get_plain_poly(&plain));
+  free(t0);
+  free(t1);
 }

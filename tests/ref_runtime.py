@@ -49,6 +49,12 @@ class RefRuntime:
         lib.Ref_rotate.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int32, C.c_void_p, C.c_void_p]
         lib.Ref_mul_relin_rescale.argtypes = [C.c_void_p] * 4 + [C.c_size_t] + [C.c_void_p] * 2
         lib.Ref_relinearize.argtypes = [C.c_void_p] * 3 + [C.c_size_t] + [C.c_void_p] * 2
+        lib.Ref_export_key.argtypes = [C.c_int, C.c_void_p]
+        lib.Ref_encode.argtypes = [C.c_void_p, C.c_size_t, C.c_uint32, C.c_uint32, C.c_void_p]
+        lib.Ref_encode_scalar.argtypes = [C.c_double, C.c_uint32, C.c_uint32, C.c_void_p]
+        lib.Ref_encrypt.argtypes = [C.c_void_p, C.c_size_t, C.c_uint32, C.c_void_p, C.c_void_p]
+        lib.Ref_decrypt_decode.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint32,
+                                           C.c_void_p, C.c_size_t]
         for name in ("Hw_modadd", "Hw_modsub", "Hw_modmul", "Hw_modmuladd", "Hw_rotate"):
             getattr(lib, name).restype = C.c_void_p
         lib.Hw_modadd.argtypes = lib.Hw_modsub.argtypes = lib.Hw_modmul.argtypes = \
@@ -168,6 +174,51 @@ class RefRuntime:
         o0 = np.zeros((level, self.N), np.int64); o1 = np.zeros_like(o0)
         self.lib.Ref_relinearize(*[_p(x) for x in arrs], level, _p(o0), _p(o1))
         return o0, o1
+
+
+def _client(self):
+    pass
+
+
+def export_key(self, which):
+    limbs = self.L + self.K if which < 2 else self.L
+    out = np.zeros((limbs, self.N), np.int64)
+    self.lib.Ref_export_key(which, _p(out))
+    return out
+
+
+def encode(self, values, sf_degree=1, level=0):
+    v = np.ascontiguousarray(np.asarray(values, dtype=np.complex128))
+    lv = level or self.L
+    out = np.zeros((lv, self.N), np.int64)
+    self.lib.Ref_encode(_p(v.view(np.float64)), len(v), sf_degree, lv, _p(out))
+    return out
+
+
+def encode_scalar(self, value, sf_degree=1, level=0):
+    lv = level or self.L
+    out = np.zeros((lv, self.N), np.int64)
+    self.lib.Ref_encode_scalar(float(value), sf_degree, lv, _p(out))
+    return out
+
+
+def encrypt(self, plain_poly, sf_degree=1):
+    pp = np.ascontiguousarray(plain_poly, np.int64)
+    c0 = np.zeros_like(pp); c1 = np.zeros_like(pp)
+    self.lib.Ref_encrypt(_p(pp), pp.shape[0], sf_degree, _p(c0), _p(c1))
+    return c0, c1
+
+
+def decrypt_decode(self, c0, c1, sf_degree=1, count=None):
+    c0 = np.ascontiguousarray(c0, np.int64); c1 = np.ascontiguousarray(c1, np.int64)
+    count = count or self.N // 2
+    out = np.zeros(count, np.complex128)
+    self.lib.Ref_decrypt_decode(_p(c0), _p(c1), c0.shape[0], sf_degree, _p(out.view(np.float64)), count)
+    return out
+
+
+for _f in (export_key, encode, encode_scalar, encrypt, decrypt_decode):
+    setattr(RefRuntime, _f.__name__, _f)
 
 
 def uniform_limbs(rng, primes, n):

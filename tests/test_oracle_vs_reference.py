@@ -95,3 +95,22 @@ def test_live_reference_n2048():
     finally:
         orc.close()
         rr.close_ref(ref)
+
+
+@pytest.mark.skipif(not rr.available(), reason="reference runtime not built")
+@pytest.mark.parametrize("params", [(16, 4, 60, 59), (16384, 3, 60, 56), (16, 3, 33, 30)])
+def test_root_table_rule_matches_reference(params):
+    """ring degrees 16 and 16384 take some 2N-th roots from the reference's table
+    (util/src/std_param.c:229-300); the oracle reproduces the rule behind it"""
+    n, L, q0, sf = params
+    ref = rr.RefRuntime(n, L, q0, sf, 2, rot_idxs=(1,), seed=np.arange(16))
+    orc = oracle_lib.Oracle(n, L, q0, sf, 2)
+    try:
+        assert orc.primes == ref.primes
+        for i in range(orc.L + orc.K):
+            rou, inv, _ = orc.tables(i)
+            e_rou, _, e_inv, _, _ = ref.ntt_tables(i)
+            assert np.array_equal(rou, e_rou) and np.array_equal(inv, e_inv), i
+    finally:
+        orc.close()
+        rr.close_ref(ref)
