@@ -158,6 +158,37 @@ SIGNATURES = {
     "Init_ciph_down_scale": (None, [CIPHER, CIPHER]),
     "Init_ciph3_up_scale": (None, [CIPHER3, CIPHER, CIPHER]),
     "Copy_ciph": (None, [CIPHER, CIPHER]),
+    "Init_ciph_same_scale_plain": (None, [CIPHER, CIPHER, PLAIN]),
+    "Init_ciph_same_scale_ciph3": (None, [CIPHER, CIPHER3]),
+    "Init_ciph3_same_scale_ciph3": (None, [CIPHER3, CIPHER3, CIPHER3]),
+    "Init_ciph3_same_scale": (None, [CIPHER3, CIPHER3, CIPHER3]),
+    "Init_ciph_up_scale_plain": (None, [CIPHER, CIPHER, PLAIN]),
+    "Init_ciph3_down_scale": (None, [CIPHER3, CIPHER3]),
+    "Zero_ciph": (None, [CIPHER]),
+    "Sc_degree": (C.c_uint32, [CIPHER]),
+    "Get_slots": (C.c_uint32, [CIPHER]),
+    "Set_slots": (None, [CIPHER, C.c_uint32]),
+    "Poly_level": (C.c_size_t, [POLY]),
+    "Num_p": (C.c_size_t, [POLY]),
+    "Num_alloc": (C.c_size_t, [POLY]),
+    # program driver
+    "Get_rt_data_info": (C.c_void_p, []),
+    "Get_input_count": (C.c_int, []),
+    "Get_output_count": (C.c_int, []),
+    "Get_encode_scheme": (C.c_void_p, [C.c_int]),
+    "Get_decode_scheme": (C.c_void_p, [C.c_int]),
+    "Main_graph": (C.c_bool, []),
+    "Alloc_tensor": (C.c_void_p, [C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t,
+                                  C.POINTER(C.c_double)]),
+    "Free_tensor": (None, [C.c_void_p]),
+    "Print_tensor": (None, [C.c_void_p, C.c_void_p]),
+    "Prepare_input": (None, [C.c_void_p, C.c_char_p]),
+    "Get_input_data": (CIPHERTEXT, [C.c_char_p, C.c_size_t]),
+    "Set_output_data": (None, [C.c_char_p, C.c_size_t, CIPHER]),
+    "Run_main_graph": (None, []),
+    "Handle_output": (C.POINTER(C.c_double), [C.c_char_p]),
+    "Tm_start": (None, [C.c_char_p]),
+    "Tm_taken": (None, [C.c_char_p]),
     "Level": (C.c_size_t, [CIPHER]),
     "Free_ciph_poly": (None, [CIPHER, C.c_uint32]),
     "Add_ciph": (CIPHER, [CIPHER, CIPHER, CIPHER]),

@@ -119,7 +119,7 @@ void Prepare_context(void) {
       "_first_mod_size = %ld, _scaling_mod_size = %ld, _num_q_parts = %ld, _num_p = %ld, "
       "_num_rot_idx = %ld,_hamming_weight = %ld\n",
       (int)p->_provider, (int)p->_poly_degree, (long)p->_mul_depth, (long)p->_input_level,
-      (long)p->_first_mod_size, (long)p->_scaling_mod_size, (long)p->_num_q_parts,
+      (long)p->_first_mod_size, (long)p->_scaling_mod_size, (long)c->dnum,
       (long)c->K, (long)p->_num_rot_idx, (long)p->_hamming_weight);
 }
 
@@ -746,29 +746,15 @@ static void init_ciph(CIPHER res, uint32_t degree, size_t level, size_t num_p, d
   res->_slots           = slots;
 }
 
-void Init_ciph_same_scale(CIPHER res, CIPHER a, CIPHER b) {
+// shape of the lower-level operand; the public Init_ciph_* family with the
+// reference's storage-reuse rules lives in program_api.cu
+static void init_like_lower(CIPHER res, CIPHER a, CIPHER b) {
   CIPHER low = (b != nullptr && Level(b) < Level(a)) ? b : a;
-  if (low->_c0_poly._data == nullptr) {
-    std::memset(res, 0, sizeof(CIPHERTEXT));
-    return;
-  }
   init_ciph(res, low->_c0_poly._ring_degree, Level(low), low->_c0_poly._num_primes_p,
             low->_scaling_factor, low->_sf_degree, low->_slots);
 }
 
-void Init_ciph_up_scale(CIPHER res, CIPHER a, CIPHER b) {
-  CIPHER low = Level(b) < Level(a) ? b : a;
-  init_ciph(res, low->_c0_poly._ring_degree, Level(low), low->_c0_poly._num_primes_p,
-            a->_scaling_factor * b->_scaling_factor, a->_sf_degree + b->_sf_degree, low->_slots);
-}
-
-void Init_ciph_down_scale(CIPHER res, CIPHER a) {
-  FHERT_ASSERT(a->_sf_degree >= 2, "Scale degree of result dec to zero");
-  init_ciph(res, a->_c0_poly._ring_degree, Level(a), a->_c0_poly._num_primes_p,
-            a->_scaling_factor / Get_default_sc(), a->_sf_degree - 1, a->_slots);
-}
-
-void Init_ciph3_up_scale(CIPHER3 res, CIPHER a, CIPHER b) {
+static void init_ciph3_product(CIPHER3 res, CIPHER a, CIPHER b) {
   CIPHER low   = Level(b) < Level(a) ? b : a;
   uint32_t deg = low->_c0_poly._ring_degree;
   for (POLYNOMIAL* p : {&res->_c0_poly, &res->_c1_poly, &res->_c2_poly}) {
@@ -780,17 +766,9 @@ void Init_ciph3_up_scale(CIPHER3 res, CIPHER a, CIPHER b) {
   res->_slots          = low->_slots;
 }
 
-void Copy_ciph(CIPHER res, CIPHER ciph) {
-  if (res == ciph) return;
-  init_ciph(res, ciph->_c0_poly._ring_degree, Level(ciph), ciph->_c0_poly._num_primes_p,
-            ciph->_scaling_factor, ciph->_sf_degree, ciph->_slots);
-  Copy_poly(&res->_c0_poly, &ciph->_c0_poly);
-  Copy_poly(&res->_c1_poly, &ciph->_c1_poly);
-}
-
 static CIPHER add_sub_ciph(EwOp op, CIPHER res, CIPHER a, CIPHER b) {
   Context* c = ctx();
-  Init_ciph_same_scale(res, a, b);
+  init_like_lower(res, a, b);
   size_t level = Level(res), num_p = res->_c0_poly._num_primes_p;
   FHERT_ASSERT(num_p == 0 || (a->_c0_poly._num_primes_p == num_p && b->_c0_poly._num_primes_p == num_p),
                "unmatched special limbs");
@@ -806,7 +784,7 @@ CIPHER Sub_ciph(CIPHER res, CIPHER a, CIPHER b) { return add_sub_ciph(EW_SUB, re
 
 CIPHER3 Mul_ciph3(CIPHER3 res, CIPHER a, CIPHER b) {
   // evaluator.c:137-173: c0 = a0*b0, c1 = a0*b1 + a1*b0, c2 = a1*b1
-  Init_ciph3_up_scale(res, a, b);
+  init_ciph3_product(res, a, b);
   size_t level = res->_c0_poly._num_primes;
   launch_tensor(res->_c0_poly._data, res->_c1_poly._data, res->_c2_poly._data,
                 a->_c0_poly._data, a->_c1_poly._data, b->_c0_poly._data, b->_c1_poly._data,

@@ -359,6 +359,8 @@ Context* create_context(const CKKS_PARAMS* p) {
   c->logN           = 31 - __builtin_clz(c->N);
   c->L              = (int)p->_mul_depth + 1;
   c->dnum           = (int)p->_num_q_parts;
+  // util/src/std_param.c:356-363: digit count when the program leaves it open
+  if (c->dnum == 0) c->dnum = p->_mul_depth > 3 ? 3 : (p->_mul_depth == 0 ? 1 : 2);
   c->q0_bits        = p->_first_mod_size;
   c->sf_bits        = p->_scaling_mod_size;
   c->hamming_weight = p->_hamming_weight;

@@ -1,0 +1,387 @@
+// Entry points a compiled program and its driver use around the arithmetic:
+// ciphertext metadata initialisers, accessors, tensors, program input/output
+// and the per-operator timer.  Semantics follow the CPU runtime function of
+// the same name; citations name files inside fhe-cmplr/rtlib/.
+#include <cstring>
+#include <ctime>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "runtime.h"
+
+using namespace fhert;
+
+namespace {
+
+// ant/poly/src/rns_poly.c:18-37: shape res like poly; reuse res's storage when
+// large enough (cleared), else allocate zero-filled storage
+void init_poly_like(POLY res, POLY poly) {
+  if (poly == res) return;
+  uint32_t n   = poly->_ring_degree;
+  size_t   q   = poly->_num_primes, p = poly->_num_primes_p;
+  if (res->_data == nullptr) {
+    Alloc_poly_data(res, n, q, p);
+  } else if (res->_num_alloc_primes < q + p) {
+    Free_poly_data(res);
+    Alloc_poly_data(res, n, q, p);
+  } else {
+    CUDA_CHECK(cudaMemsetAsync(res->_data, 0,
+                               res->_num_alloc_primes * (size_t)n * sizeof(int64_t),
+                               ctx()->stream));
+    res->_ring_degree  = n;
+    res->_num_primes   = q;
+    res->_num_primes_p = p;
+  }
+  res->_is_ntt = poly->_is_ntt;
+}
+
+void set_level(POLY p, size_t level) {
+  FHERT_ASSERT(p->_num_alloc_primes >= level + p->_num_primes_p, "raised level exceed alloc_size");
+  p->_num_primes = level;
+}
+
+// ant/include/ckks/ciphertext.h:109-135: contents are kept when storage exists
+void init_ciphertext(CIPHER res, uint32_t n, size_t level, size_t num_p, double sf,
+                     uint32_t sf_degree, uint32_t slots) {
+  res->_scaling_factor = sf;
+  res->_sf_degree      = sf_degree;
+  res->_slots          = slots;
+  for (POLY p : {&res->_c0_poly, &res->_c1_poly}) {
+    if (p->_data == nullptr) {
+      Alloc_poly_data(p, n, level, num_p);
+    } else {
+      FHERT_ASSERT(p->_ring_degree == n, "unmatched ciphertxt");
+      set_level(p, level);
+    }
+  }
+}
+
+// ciphertext.h:137-147
+void init_from_ciph(CIPHER res, CIPHER ciph, double sf, uint32_t sf_degree) {
+  res->_scaling_factor = sf;
+  res->_sf_degree      = sf_degree;
+  res->_slots          = ciph->_slots;
+  if (res == ciph) return;
+  init_poly_like(&res->_c0_poly, &ciph->_c0_poly);
+  init_poly_like(&res->_c1_poly, &ciph->_c1_poly);
+}
+
+// ciphertext.h:203-238 without resizing: the operand of lower level
+CIPHER lower_level(CIPHER a, CIPHER b) {
+  if (a->_c0_poly._data == nullptr) return b;
+  FHERT_ASSERT(b->_c0_poly._data != nullptr, "poly coeffs of input ciph is invalid");
+  return a->_c0_poly._num_primes > b->_c0_poly._num_primes ? b : a;
+}
+
+CIPHER3 lower_level3(CIPHER3 a, CIPHER3 b) {
+  if (a->_c0_poly._data == nullptr) return b;
+  FHERT_ASSERT(b->_c0_poly._data != nullptr, "poly coeffs of input ciph is invalid");
+  return a->_c0_poly._num_primes > b->_c0_poly._num_primes ? b : a;
+}
+
+// ant/ckks/src/cipher.c:27-34
+void init_cipher(CIPHER res, CIPHER ciph, double sf, uint32_t sf_degree) {
+  init_from_ciph(res, ciph, sf, sf_degree);
+  res->_c0_poly._is_ntt = res->_c1_poly._is_ntt = true;
+  set_level(&res->_c0_poly, ciph->_c0_poly._num_primes);
+  set_level(&res->_c1_poly, ciph->_c0_poly._num_primes);
+}
+
+void init_ciph3_from(CIPHER3 res, POLY c0, POLY c1, POLY c2, double sf, uint32_t sf_degree,
+                     uint32_t slots) {
+  res->_scaling_factor = sf;
+  res->_sf_degree      = sf_degree;
+  res->_slots          = slots;
+  init_poly_like(&res->_c0_poly, c0);
+  init_poly_like(&res->_c1_poly, c1);
+  init_poly_like(&res->_c2_poly, c2);
+  for (POLY p : {&res->_c0_poly, &res->_c1_poly, &res->_c2_poly}) p->_is_ntt = true;
+}
+
+struct IoTable {
+  std::map<std::string, std::vector<CIPHERTEXT*>> inputs, outputs;
+};
+IoTable g_io;
+
+CIPHERTEXT* new_ciph() { return (CIPHERTEXT*)std::calloc(1, sizeof(CIPHERTEXT)); }
+
+clock_t g_tm_stamp = 0;
+
+}  // namespace
+
+extern "C" {
+
+// ---- program-supplied hooks (include/common/rt_api.h:48-80), weak so that a
+// host without a compiled program still links
+__attribute__((weak)) DATA_SCHEME* Get_encode_scheme(int) { return nullptr; }
+__attribute__((weak)) DATA_SCHEME* Get_decode_scheme(int) { return nullptr; }
+__attribute__((weak)) RT_DATA_INFO* Get_rt_data_info(void) { return nullptr; }
+__attribute__((weak)) int           Get_input_count(void) { return 0; }
+__attribute__((weak)) int           Get_output_count(void) { return 0; }
+__attribute__((weak)) bool          Main_graph(void) { return false; }
+
+// ---- accessors (ant/include/poly/rns_poly.h:41-66, ant/ckks/src/cipher.c:164-170)
+size_t   Poly_level(POLY poly) { return poly->_num_primes; }
+size_t   Num_p(POLY poly) { return poly->_num_primes_p; }
+size_t   Num_alloc(POLY poly) { return poly->_num_alloc_primes; }
+uint32_t Sc_degree(CIPHER ciph) { return ciph->_sf_degree; }
+uint32_t Get_slots(CIPHER ciph) { return ciph->_slots; }
+void     Set_slots(CIPHER ciph, uint32_t slots) { ciph->_slots = slots; }
+
+// ---- metadata initialisers (ant/ckks/src/cipher.c:36-156)
+void Init_ciph_same_scale(CIPHER res, CIPHER ciph1, CIPHER ciph2) {
+  CIPHER ciph = ciph2 != nullptr ? lower_level(ciph1, ciph2) : ciph1;
+  if (ciph == ciph2 && ciph1->_c0_poly._data == nullptr) {
+    init_from_ciph(ciph1, ciph2, ciph2->_scaling_factor, ciph2->_sf_degree);
+  } else if (ciph->_c0_poly._data == nullptr) {
+    std::memset(res, 0, sizeof(CIPHERTEXT));
+    return;
+  }
+  init_ciphertext(res, ciph->_c0_poly._ring_degree, ciph->_c0_poly._num_primes,
+                  ciph->_c0_poly._num_primes_p, ciph->_scaling_factor, ciph->_sf_degree,
+                  ciph->_slots);
+  res->_c0_poly._is_ntt = res->_c1_poly._is_ntt = true;
+}
+
+void Init_ciph_same_scale_plain(CIPHER res, CIPHER ciph, PLAIN plain) {
+  init_cipher(res, ciph, ciph->_scaling_factor, ciph->_sf_degree);
+  size_t pl = plain->_poly._num_primes;
+  if (ciph->_c0_poly._num_primes > pl) {
+    set_level(&res->_c0_poly, pl);
+    set_level(&res->_c1_poly, pl);
+  }
+}
+
+void Init_ciph_up_scale(CIPHER res, CIPHER ciph1, CIPHER ciph2) {
+  CIPHER ciph = lower_level(ciph1, ciph2);
+  init_cipher(res, ciph, ciph1->_scaling_factor * ciph2->_scaling_factor,
+              ciph1->_sf_degree + ciph2->_sf_degree);
+}
+
+void Init_ciph_up_scale_plain(CIPHER res, CIPHER ciph, PLAIN plain) {
+  init_cipher(res, ciph, ciph->_scaling_factor * plain->_scaling_factor,
+              ciph->_sf_degree + plain->_sf_degree);
+  size_t pl = plain->_poly._num_primes;
+  if (ciph->_c0_poly._num_primes > pl) {
+    set_level(&res->_c0_poly, pl);
+    set_level(&res->_c1_poly, pl);
+  }
+}
+
+void Init_ciph_down_scale(CIPHER res, CIPHER ciph) {
+  FHERT_ASSERT(ciph->_sf_degree >= 2, "Scale degree of result dec to zero");
+  init_cipher(res, ciph, ciph->_scaling_factor / Get_default_sc(), ciph->_sf_degree - 1);
+}
+
+void Init_ciph3_down_scale(CIPHER3 res, CIPHER3 ciph) {
+  FHERT_ASSERT(ciph->_sf_degree >= 2, "Scale degree of result dec to zero");
+  res->_scaling_factor = ciph->_scaling_factor / Get_default_sc();
+  res->_sf_degree      = ciph->_sf_degree - 1;
+  res->_slots          = ciph->_slots;
+  init_poly_like(&res->_c0_poly, &ciph->_c0_poly);
+  init_poly_like(&res->_c1_poly, &ciph->_c1_poly);
+  init_poly_like(&res->_c2_poly, &ciph->_c2_poly);
+}
+
+void Init_ciph_same_scale_ciph3(CIPHER res, CIPHER3 ciph) {
+  res->_scaling_factor = ciph->_scaling_factor;
+  res->_sf_degree      = ciph->_sf_degree;
+  res->_slots          = ciph->_slots;
+  init_poly_like(&res->_c0_poly, &ciph->_c0_poly);
+  init_poly_like(&res->_c1_poly, &ciph->_c1_poly);
+  res->_c0_poly._is_ntt = res->_c1_poly._is_ntt = true;
+  set_level(&res->_c0_poly, ciph->_c0_poly._num_primes);
+  set_level(&res->_c1_poly, ciph->_c0_poly._num_primes);
+}
+
+void Init_ciph3_same_scale_ciph3(CIPHER3 res, CIPHER3 ciph1, CIPHER3 ciph2) {
+  CIPHER3 ciph = ciph2 != nullptr ? lower_level3(ciph1, ciph2) : ciph1;
+  init_ciph3_from(res, &ciph->_c0_poly, &ciph->_c1_poly, &ciph->_c2_poly,
+                  ciph->_scaling_factor, ciph->_sf_degree, ciph->_slots);
+}
+
+void Init_ciph3_same_scale(CIPHER3 res, CIPHER3 ciph1, CIPHER3 ciph2) {
+  Init_ciph3_same_scale_ciph3(res, ciph1, ciph2);
+}
+
+void Init_ciph3_up_scale(CIPHER3 res, CIPHER ciph1, CIPHER ciph2) {
+  CIPHER ciph = lower_level(ciph1, ciph2);
+  FHERT_ASSERT(ciph->_c0_poly._num_primes_p == 0, "invalid num of p primes");
+  init_ciph3_from(res, &ciph->_c0_poly, &ciph->_c0_poly, &ciph->_c0_poly,
+                  ciph1->_scaling_factor * ciph2->_scaling_factor,
+                  ciph1->_sf_degree + ciph2->_sf_degree, ciph->_slots);
+}
+
+void Copy_ciph(CIPHER res, CIPHER ciph) {
+  init_from_ciph(res, ciph, ciph->_scaling_factor, ciph->_sf_degree);
+  Copy_poly(&res->_c0_poly, &ciph->_c0_poly);
+  Copy_poly(&res->_c1_poly, &ciph->_c1_poly);
+}
+
+void Zero_ciph(CIPHER ciph) {
+  Free_poly_data(&ciph->_c0_poly);
+  Free_poly_data(&ciph->_c1_poly);
+  std::memset(ciph, 0, sizeof(*ciph));
+}
+
+// ---- tensors (common/src/tensor.c)
+TENSOR* Alloc_tensor(size_t n, size_t c, size_t h, size_t w, const double* vals) {
+  size_t  bytes = n * c * h * w * sizeof(double);
+  TENSOR* t     = (TENSOR*)std::malloc(sizeof(TENSOR) + bytes);
+  t->_shape._n  = n;
+  t->_shape._c  = c;
+  t->_shape._h  = h;
+  t->_shape._w  = w;
+  if (vals) std::memcpy(t->_vals, vals, bytes);
+  else std::memset(t->_vals, 0, bytes);
+  return t;
+}
+
+void Free_tensor(TENSOR* tensor) { std::free(tensor); }
+
+void Print_tensor(FILE* fp, TENSOR* t) {
+  std::fprintf(fp, "(tensor): [\n");
+  for (size_t n = 0; n < t->_shape._n; n++) {
+    if (n) std::fprintf(fp, "\n");
+    for (size_t c = 0; c < t->_shape._c; c++) {
+      if (c) std::fprintf(fp, "\n");
+      for (size_t h = 0; h < t->_shape._h; h++) {
+        if (h) std::fprintf(fp, "\n");
+        for (size_t w = 0; w < t->_shape._w; w++)
+          std::fprintf(fp, " %f",
+                       t->_vals[w + t->_shape._w * (h + t->_shape._h * (c + t->_shape._c * n))]);
+      }
+    }
+  }
+  std::fprintf(fp, "\n]\n");
+  std::fflush(stdout);
+}
+
+// ---- timer (common/src/rt_stat.c:23-31); scripts parse this line format
+void Tm_start(const char*) { g_tm_stamp = clock(); }
+
+void Tm_taken(const char* msg) {
+  Fhert_sync();  // the queued kernels belong to the operator being timed
+  clock_t now = clock();
+  std::fprintf(stdout, "[RT_STAT] %s takes %.3f seconds.\n", msg,
+               ((double)(now - g_tm_stamp)) / (double)CLOCKS_PER_SEC);
+  g_tm_stamp = now;
+  std::fflush(stdout);
+}
+
+// ---- program input / output (ant/ckks/src/rtlib.c:164-244)
+void Prepare_input(TENSOR* input, const char* name) {
+  Context*     c      = ctx();
+  DATA_SCHEME* scheme = nullptr;
+  for (int i = 0; i < Get_input_count(); i++) {
+    DATA_SCHEME* s = Get_encode_scheme(i);
+    FHERT_ASSERT(s != nullptr, "invalid encode scheme");
+    if (std::strcmp(s->_name, name) == 0) {
+      scheme = s;
+      break;
+    }
+  }
+  FHERT_ASSERT(scheme != nullptr && scheme->_count > 0, "not find the input");
+  size_t total = input->_shape._n * input->_shape._c * input->_shape._h * input->_shape._w;
+  size_t hw    = input->_shape._h * input->_shape._w;
+  for (int i = 0; i < scheme->_count; i++) {
+    const MAP_DESC*     d = &scheme->_desc[i];
+    std::vector<double> vec;
+    if (d->_count == 0) {
+      vec.assign(input->_vals, input->_vals + total);
+    } else {
+      FHERT_ASSERT(d->_kind == NORMAL && d->_stride == 1, "TODO: other kind");
+      size_t loc   = d->_start;
+      bool   begin = (loc % hw) == 0, end = ((loc + (size_t)d->_count * d->_stride) % hw) == 0;
+      vec.resize(d->_count + 2 * d->_pad);
+      for (int k = 0; k < d->_pad; k++)
+        vec[k] = begin ? 0 : input->_vals[loc - (size_t)(d->_pad - k) * d->_stride];
+      for (int k = 0; k < d->_count; k++, loc += d->_stride) vec[k + d->_pad] = input->_vals[loc];
+      for (int k = 0; k < d->_pad; k++)
+        vec[k + d->_pad + d->_count] = end ? 0 : input->_vals[loc + (size_t)k * d->_stride];
+    }
+    PLAINTEXT plain;
+    std::memset(&plain, 0, sizeof(plain));
+    // a one-element tensor still goes through the vector encoder here
+    // (rtlib.c:181 calls the encoder directly, not Encode_double)
+    std::vector<double> pairs(2 * vec.size(), 0.0);
+    for (size_t k = 0; k < vec.size(); k++) pairs[2 * k] = vec[k];
+    Encode_dcmplx(&plain, pairs.data(), vec.size(), 1, (uint32_t)c->input_level);
+    CIPHERTEXT* ciph = new_ciph();
+    Encrypt(ciph, &plain);
+    Free_plain_data(&plain);
+    auto& slot = g_io.inputs[name];
+    if (slot.size() <= (size_t)i) slot.resize(i + 1, nullptr);
+    slot[i] = ciph;
+  }
+}
+
+CIPHERTEXT Get_input_data(const char* name, size_t idx) {
+  auto it = g_io.inputs.find(name);
+  FHERT_ASSERT(it != g_io.inputs.end() && idx < it->second.size() && it->second[idx],
+               "not find data");
+  CIPHERTEXT ret  = *it->second[idx];
+  std::free(it->second[idx]);  // the polynomials now belong to the caller
+  it->second[idx] = nullptr;
+  return ret;
+}
+
+void Set_output_data(const char* name, size_t idx, CIPHER data) {
+  CIPHERTEXT* out = new_ciph();
+  Copy_ciph(out, data);
+  Free_ciph_poly(data, 1);
+  auto& slot = g_io.outputs[name];
+  if (slot.size() <= idx) slot.resize(idx + 1, nullptr);
+  slot[idx] = out;
+}
+
+void Run_main_graph(void) {
+  bool ok = Main_graph();
+  FHERT_ASSERT(ok, "run Main_graph failed");
+}
+
+double* Handle_output(const char* name) {
+  Context*     c      = ctx();
+  DATA_SCHEME* scheme = nullptr;
+  for (int i = 0; i < Get_output_count(); i++) {
+    DATA_SCHEME* s = Get_decode_scheme(i);
+    FHERT_ASSERT(s != nullptr, "invalid encode scheme");
+    if (std::strcmp(s->_name, name) == 0) {
+      scheme = s;
+      break;
+    }
+  }
+  FHERT_ASSERT(scheme != nullptr && scheme->_count > 0, "not find the output");
+  size_t len = scheme->_shape._n * scheme->_shape._c * scheme->_shape._h * scheme->_shape._w;
+  if (len == 0) len = c->N / 2;
+  double* ret = (double*)std::calloc(len, sizeof(double));
+  auto    it  = g_io.outputs.find(name);
+  FHERT_ASSERT(it != g_io.outputs.end(), "not find data");
+  for (int i = 0; i < scheme->_count; i++) {
+    FHERT_ASSERT((size_t)i < it->second.size() && it->second[i], "not find data");
+    CIPHERTEXT* ciph = it->second[i];
+    PLAINTEXT   plain;
+    std::memset(&plain, 0, sizeof(plain));
+    Fhert_decrypt(&plain, ciph);
+    size_t              slots = plain._slots;
+    std::vector<double> vals(2 * slots);
+    Fhert_decode(&plain, vals.data(), slots);
+    const MAP_DESC* d = &scheme->_desc[i];
+    if (d->_count == 0) {
+      size_t out_len = slots < len ? slots : len;
+      for (size_t k = 0; k < out_len; k++) ret[k] = vals[2 * k];
+    } else {
+      FHERT_ASSERT((size_t)d->_count <= len && d->_kind == NORMAL, "chunk out of image bound");
+      size_t loc = d->_start;
+      for (int k = 0; k < d->_count; k++, loc += d->_stride) ret[loc] = vals[2 * k];
+    }
+    Free_plain_data(&plain);
+    Free_ciph_poly(ciph, 1);
+    std::free(ciph);
+    it->second[i] = nullptr;
+  }
+  return ret;
+}
+
+}  // extern "C"

@@ -28,6 +28,7 @@
 #include <stdbool.h>
 #include <stddef.h>
 #include <stdint.h>
+#include <stdio.h>
 
 #ifdef __cplusplus
 extern "C" {
@@ -98,7 +99,7 @@ typedef struct {
 typedef SWITCH_KEY* SW_KEY;
 
 /* include/common/common.h:73-85 */
-typedef enum { LIB_ANT = 0 } LIB_PROV;
+typedef enum { LIB_ANT = 0, LIB_SEAL, LIB_OPENFHE, LIB_PHANTOM, LIB_ACE } LIB_PROV;
 typedef struct {
   LIB_PROV _provider;
   uint32_t _poly_degree;
@@ -112,6 +113,45 @@ typedef struct {
   size_t   _num_rot_idx;
   int32_t  _rot_idxs[];
 } CKKS_PARAMS;
+
+/* Program input/output descriptions (include/common/common.h:23-71,
+ * include/common/tensor.h:22-25).  A compiled program hands these to the
+ * library through the Get_*_scheme hooks below; field order is part of the
+ * interface because programs initialise them positionally. */
+typedef enum { NORMAL = 0, CONV, CHANNEL, DIAGONAL } MAP_KIND;
+typedef enum { DE_MSG_F32 = 0, DE_MSG_F64, DE_PLAINTEXT } DATA_ENTRY_TYPE;
+typedef struct {
+  MAP_KIND _kind;   /* only NORMAL is handled, as in the CPU runtime */
+  int      _count;  /* elements of this ciphertext; 0 = the whole tensor */
+  int      _start;
+  int      _pad;    /* elements repeated before and after the chunk */
+  int      _stride;
+} MAP_DESC;
+typedef struct {
+  size_t _n, _c, _h, _w;
+} SHAPE;
+typedef struct {
+  const char* _name;
+  SHAPE       _shape;
+  int         _count; /* ciphertexts this tensor is split into */
+  MAP_DESC*   _desc;
+} DATA_SCHEME;
+typedef struct {
+  const char*     _file_name;
+  const char*     _file_uuid;
+  DATA_ENTRY_TYPE _entry_type;
+} RT_DATA_INFO;
+typedef struct {
+  SHAPE  _shape;
+  double _vals[];
+} TENSOR;
+
+#ifndef TRUE
+#define TRUE 1
+#endif
+#ifndef FALSE
+#define FALSE 0
+#endif
 
 /* ------------------------------------------------------------------------ */
 /* Context  (ant/context/src/ckks_context.c:84-217, ant/util/src/crt.c)      */
@@ -300,11 +340,29 @@ void Fhert_export_key(int which, int64_t* host);
 /* Ciphertext level  (ant/ckks/src/cipher.c, evaluator.c)                    */
 /* ------------------------------------------------------------------------ */
 
-void   Init_ciph_same_scale(CIPHER res, CIPHER a, CIPHER b);      /* cipher.c:36 */
-void   Init_ciph_up_scale(CIPHER res, CIPHER a, CIPHER b);        /* cipher.c:96 */
-void   Init_ciph_down_scale(CIPHER res, CIPHER a);                /* cipher.c:131 */
-void   Init_ciph3_up_scale(CIPHER3 res, CIPHER a, CIPHER b);      /* cipher.c:118 */
-void   Copy_ciph(CIPHER res, CIPHER ciph);                        /* cipher.c:158 */
+/* Result shaping done by a compiled program before it fills the limbs
+ * (ant/ckks/src/cipher.c:27-156, ant/include/ckks/ciphertext.h:109-238).
+ * Storage that res already owns is reused when it is large enough: the
+ * two-polynomial initialisers keep its contents, the ones that shape res
+ * after another object clear it. */
+void Init_ciph_same_scale(CIPHER res, CIPHER a, CIPHER b);          /* cipher.c:36, b may be NULL */
+void Init_ciph_same_scale_plain(CIPHER res, CIPHER a, PLAIN b);     /* cipher.c:51 */
+void Init_ciph_same_scale_ciph3(CIPHER res, CIPHER3 ciph);          /* cipher.c:64 */
+void Init_ciph3_same_scale_ciph3(CIPHER3 res, CIPHER3 a, CIPHER3 b); /* cipher.c:77 */
+void Init_ciph3_same_scale(CIPHER3 res, CIPHER3 a, CIPHER3 b);
+void Init_ciph_up_scale(CIPHER res, CIPHER a, CIPHER b);            /* cipher.c:96 */
+void Init_ciph_up_scale_plain(CIPHER res, CIPHER a, PLAIN b);       /* cipher.c:105 */
+void Init_ciph3_up_scale(CIPHER3 res, CIPHER a, CIPHER b);          /* cipher.c:118 */
+void Init_ciph_down_scale(CIPHER res, CIPHER a);                    /* cipher.c:131 */
+void Init_ciph3_down_scale(CIPHER3 res, CIPHER3 a);                 /* cipher.c:144 */
+void Copy_ciph(CIPHER res, CIPHER ciph);                            /* cipher.c:158 */
+void Zero_ciph(CIPHER ciph);
+uint32_t Sc_degree(CIPHER ciph);                                    /* cipher.c:164 */
+uint32_t Get_slots(CIPHER ciph);
+void     Set_slots(CIPHER ciph, uint32_t slots);
+size_t   Poly_level(POLY poly);  /* ant/include/poly/rns_poly.h:41-66 */
+size_t   Num_p(POLY poly);
+size_t   Num_alloc(POLY poly);
 size_t Level(CIPHER ciph);
 void   Free_ciph_poly(CIPHER ciph, uint32_t cnt);
 CIPHER  Add_ciph(CIPHER res, CIPHER a, CIPHER b);       /* evaluator.c:47 */
@@ -315,6 +373,36 @@ CIPHER  Mul_ciph(CIPHER res, CIPHER a, CIPHER b);       /* evaluator.c:177 */
 CIPHER  Rescale_ciph(CIPHER res, CIPHER ciph);          /* evaluator.c:344 */
 CIPHER  Rotate_ciph(CIPHER res, CIPHER ciph, int32_t rot_idx); /* evaluator.c:503-530 */
 CIPHER  Conjugate_ciph(CIPHER res, CIPHER ciph);        /* evaluator.c:568 */
+
+/* ------------------------------------------------------------------------ */
+/* Program driver  (include/common/rt_api.h, ant/ckks/src/rtlib.c:164-244,   */
+/* common/src/tensor.c, common/src/rt_stat.c)                                */
+/* ------------------------------------------------------------------------ */
+
+/* Hooks the compiled program defines; the library holds weak defaults. */
+RT_DATA_INFO* Get_rt_data_info(void);
+int           Get_input_count(void);
+int           Get_output_count(void);
+DATA_SCHEME*  Get_encode_scheme(int idx);
+DATA_SCHEME*  Get_decode_scheme(int idx);
+bool          Main_graph(void);
+
+TENSOR* Alloc_tensor(size_t n, size_t c, size_t h, size_t w, const double* vals);
+void    Free_tensor(TENSOR* tensor);
+void    Print_tensor(FILE* fp, TENSOR* tensor);
+static inline float* Slice(float* vec, size_t row_idx, size_t col) { return vec + row_idx * col; }
+
+/* encode at the context's input level, encrypt, and park under name */
+void       Prepare_input(TENSOR* input, const char* name);
+CIPHERTEXT Get_input_data(const char* name, size_t idx); /* polynomials pass to the caller */
+void       Set_output_data(const char* name, size_t idx, CIPHER data); /* copies, then frees data */
+void       Run_main_graph(void);
+double*    Handle_output(const char* name);              /* malloc'ed, caller frees */
+
+/* per-operator timer; prints "[RT_STAT] <msg> takes <s> seconds." after
+ * draining the stream, so queued kernels are charged to their operator */
+void Tm_start(const char* msg);
+void Tm_taken(const char* msg);
 
 #ifdef __cplusplus
 }

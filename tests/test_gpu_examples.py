@@ -1,0 +1,40 @@
+"""The reference's own example programs, compiled unchanged against this
+repository's headers and linked with the B200 library.
+
+Each program (fhe-cmplr/rtlib/ant/example/eg_fhertlib_*.c plus the .inc body
+the compiler emitted) builds a context from its CKKS_PARAMS, encrypts a small
+tensor with Prepare_input, runs its Main_graph limb by limb through the C-ABI
+(Coeffs, Hw_modadd, Hw_modmul, Hw_rotate, Decomp, Mod_up, Mod_down, Rescale,
+Init_ciph_*, Encode_float ...), decrypts with Handle_output and compares with
+the values its author wrote down, printing "SUCESS!" (sic) when they agree to
+1e-3.  oracle/build_examples.sh makes the binaries where the reference
+checkout is present; here they are only executed.
+"""
+import os
+import subprocess
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+EXAMPLES = os.path.join(os.path.dirname(HERE), "oracle", "_ref", "examples")
+
+# programs that need entry points outside the built scope do not link and are
+# absent from the directory; every one that was built must pass
+NAMES = sorted(f for f in (os.listdir(EXAMPLES) if os.path.isdir(EXAMPLES) else [])
+               if f.startswith("eg_fhertlib_") and "." not in f)
+
+
+@pytest.mark.gpu
+def test_examples_were_built():
+    assert len(NAMES) >= 11, f"expected the example programs under {EXAMPLES}, found {NAMES}"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", NAMES)
+def test_example_program(name):
+    exe = os.path.join(EXAMPLES, name)
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    tail = (run.stdout + run.stderr)[-2000:]
+    assert run.returncode == 0, tail
+    assert "SUCESS!" in run.stdout, tail
+    assert "FAILED" not in run.stdout, tail
