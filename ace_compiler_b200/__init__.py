@@ -187,6 +187,13 @@ SIGNATURES = {
     "Set_output_data": (None, [C.c_char_p, C.c_size_t, CIPHER]),
     "Run_main_graph": (None, []),
     "Handle_output": (C.POINTER(C.c_double), [C.c_char_p]),
+    "Pt_mgr_init": (C.c_bool, [C.c_char_p]),
+    "Pt_mgr_fini": (None, []),
+    "Pt_from_msg": (C.c_void_p, [C.c_void_p, C.c_uint32, C.c_size_t, C.c_uint32, C.c_uint32]),
+    "Pt_from_msg_ofst": (C.c_void_p, [C.c_void_p, C.c_uint32, C.c_size_t, C.c_size_t, C.c_uint32,
+                                      C.c_uint32]),
+    "Free_data": (None, [C.c_void_p]),
+    "Fhert_pt_cache_stats": (None, [C.POINTER(C.c_size_t)] * 4),
     "Tm_start": (None, [C.c_char_p]),
     "Tm_taken": (None, [C.c_char_p]),
     "Level": (C.c_size_t, [CIPHER]),
@@ -239,6 +246,7 @@ class Runtime:
         """keygen=False skips key generation (switch keys are then imported);
         seed = 16 uint32 words pins the sample generator as Fhert_seed does."""
         self.lib = load()
+        previous = os.environ.get("FHERT_SKIP_KEYGEN")
         os.environ["FHERT_SKIP_KEYGEN"] = "0" if keygen else "1"
         if seed is not None:
             s = np.ascontiguousarray(seed, dtype=np.uint32)
@@ -247,7 +255,13 @@ class Runtime:
         rot = (C.c_int32 * max(1, len(rot_idxs)))(*rot_idxs)
         self.lib.Fhert_set_context_params(degree, num_q, q0_bits, sf_bits, num_q_parts,
                                           input_level, hamming_weight, len(rot_idxs), rot)
-        self.lib.Prepare_context()
+        try:
+            self.lib.Prepare_context()
+        finally:  # the switch is for this context only, not for child processes
+            if previous is None:
+                os.environ.pop("FHERT_SKIP_KEYGEN", None)
+            else:
+                os.environ["FHERT_SKIP_KEYGEN"] = previous
         self.N = self.lib.Degree()
         self.L = self.lib.Get_q_cnt()
         self.K = self.lib.Get_p_cnt()

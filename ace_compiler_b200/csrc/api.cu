@@ -114,6 +114,12 @@ void Prepare_context(void) {
   for (size_t i = 0; i < p->_num_rot_idx; i++) auto_index_for(c, p->_rot_idxs[i]);
   const char* skip = std::getenv("FHERT_SKIP_KEYGEN");
   if (!(skip != nullptr && skip[0] != '\0' && skip[0] != '0')) generate_keys(c);
+  // ckks_context.c:151-154: open the program's weight file when it names one
+  RT_DATA_INFO* info = Get_rt_data_info();
+  if (info != nullptr) {
+    bool ok = Pt_mgr_init(info->_file_name);
+    FHERT_ASSERT(ok, "cannot open data file %s", info->_file_name);
+  }
   std::printf(
       "ckks_param: _provider = %d, _poly_degree = %d, mul_depth = %ld, input_lev = %ld, "
       "_first_mod_size = %ld, _scaling_mod_size = %ld, _num_q_parts = %ld, _num_p = %ld, "
@@ -123,7 +129,11 @@ void Prepare_context(void) {
       (long)c->K, (long)p->_num_rot_idx, (long)p->_hamming_weight);
 }
 
-void Finalize_context(void) { destroy_context(); }
+void Finalize_context(void) {
+  if (ctx_or_null() == nullptr) return;
+  Pt_mgr_fini();
+  destroy_context();
+}
 
 uint32_t Degree(void) { return ctx()->N; }
 size_t   Get_q_cnt(void) { return ctx()->L; }

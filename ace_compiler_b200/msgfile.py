@@ -1,0 +1,41 @@
+"""Writer for the weight "message" files a compiled program reads through
+Pt_from_msg (layout: fhe-cmplr/include/fhe/core/rt_data_def.h:91-112).
+
+The compiler normally writes these next to the generated C file.  Synthetic
+ones stand in for them in tests and benchmarks: a 4 KiB header page, float32
+entries each aligned to 32 bytes, then the lookup table.
+"""
+import struct
+
+import numpy as np
+
+PAGE = 4096
+ALIGN_LOG2 = 5
+DE_MSG_F32 = 0
+
+
+def write_msg_file(path, entries, model=b"synthetic", uuid=b"0" * 36):
+    """entries: list of (name, float32 array, scale_degree, level)."""
+    payload = bytearray()
+    lut = bytearray()
+    for index, (name, values, scale, level) in enumerate(entries):
+        data = np.ascontiguousarray(values, dtype=np.float32).tobytes()
+        pad = (-len(payload)) % (1 << ALIGN_LOG2)
+        payload += b"\0" * pad
+        offset = PAGE + len(payload)
+        payload += data
+        packed = (scale & 0xFF) | ((level & 0xFF) << 8) | (offset << 16)
+        lut += struct.pack("<16sIIQ", name.encode()[:15], index, len(data), packed)
+    pad = (-len(payload)) % (1 << ALIGN_LOG2)
+    payload += b"\0" * pad
+    lut_ofst = PAGE + len(payload)
+    # magic, version, flag, entry type, entry alignment, count, table offset,
+    # creation time (two 64-bit words), model name, uuid
+    header = struct.pack("<8sIHBBQQqq48s40s", b"!ANTFHE\0", 0, 0, DE_MSG_F32, ALIGN_LOG2,
+                         len(entries), lut_ofst, 0, 0, model, uuid)
+    assert len(header) == 136
+    with open(path, "wb") as f:
+        f.write(header + b"\0" * (PAGE - len(header)))
+        f.write(payload)
+        f.write(lut)
+    return lut_ofst

@@ -399,6 +399,20 @@ void       Set_output_data(const char* name, size_t idx, CIPHER data); /* copies
 void       Run_main_graph(void);
 double*    Handle_output(const char* name);              /* malloc'ed, caller frees */
 
+/* Weight data file named by Get_rt_data_info (message files of floats,
+ * fhe-cmplr/include/fhe/core/rt_data_def.h:91-112; opened by Prepare_context)
+ * and the plaintexts encoded from it (ant/porting/pt_mgr.c:179-214).
+ * FHERT_PT_CACHE_MB=<n> keeps up to n MiB of encoded plaintexts resident in
+ * device memory, keyed by (entry, offset, length, scale degree, level); a
+ * cached plaintext is lent to the caller and Free_data leaves it alone. */
+bool  Pt_mgr_init(const char* fname);
+void  Pt_mgr_fini(void);
+void* Pt_from_msg(void* pt, uint32_t index, size_t len, uint32_t scale, uint32_t level);
+void* Pt_from_msg_ofst(void* pt, uint32_t index, size_t ofst, size_t len, uint32_t scale,
+                       uint32_t level);
+void  Free_data(void* poly);
+void  Fhert_pt_cache_stats(size_t* entries, size_t* bytes, size_t* hits, size_t* misses);
+
 /* per-operator timer; prints "[RT_STAT] <msg> takes <s> seconds." after
  * draining the stream, so queued kernels are charged to their operator */
 void Tm_start(const char* msg);
