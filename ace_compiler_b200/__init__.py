@@ -171,6 +171,11 @@ SIGNATURES = {
     "Poly_level": (C.c_size_t, [POLY]),
     "Num_p": (C.c_size_t, [POLY]),
     "Num_alloc": (C.c_size_t, [POLY]),
+    "Bootstrap": (CIPHER, [CIPHER, CIPHER, C.c_uint32]),
+    "Bootstrap_precom": (None, [C.c_uint32]),
+    "Fhert_bootstrap_rotations": (C.c_size_t, [C.c_uint32, C.POINTER(C.c_int32), C.c_size_t]),
+    "Fhert_export_bootstrap_plain": (C.c_size_t, [C.c_uint32, C.c_int, C.c_uint32, C.c_uint32,
+                                                  C.c_void_p]),
     # program driver
     "Get_rt_data_info": (C.c_void_p, []),
     "Get_input_count": (C.c_int, []),

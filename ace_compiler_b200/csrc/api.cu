@@ -36,6 +36,10 @@ LimbBatch single(int prime) {
   return b;
 }
 
+}  // namespace
+
+namespace fhert {
+
 // Q limbs [0, level) and, when present, the K special limbs, with the limb
 // offsets of each operand computed from its own allocation.
 LimbBatch poly_batch(Context* c, POLY res, POLY a, POLY b, size_t level, size_t num_p) {
@@ -68,7 +72,10 @@ LimbBatch both_polys(const LimbBatch& one) {
 }
 
 void ensure_poly(POLY res, uint32_t degree, size_t num_q, size_t num_p) {
-  if (res->_data == nullptr || res->_num_alloc_primes < num_q + num_p) {
+  // special limbs live at the end of the allocation: a polynomial that has
+  // them must own exactly num_q + num_p limbs
+  if (res->_data == nullptr || (num_p ? res->_num_alloc_primes != num_q + num_p
+                                      : res->_num_alloc_primes < num_q)) {
     Free_poly_data(res);
     Alloc_poly_data(res, degree, num_q, num_p);
   } else {
@@ -78,7 +85,7 @@ void ensure_poly(POLY res, uint32_t degree, size_t num_q, size_t num_p) {
   }
 }
 
-}  // namespace
+}  // namespace fhert
 
 extern "C" {
 
@@ -113,7 +120,14 @@ void Prepare_context(void) {
   Context* c = create_context(p);
   for (size_t i = 0; i < p->_num_rot_idx; i++) auto_index_for(c, p->_rot_idxs[i]);
   const char* skip = std::getenv("FHERT_SKIP_KEYGEN");
-  if (!(skip != nullptr && skip[0] != '\0' && skip[0] != '0')) generate_keys(c);
+  if (!(skip != nullptr && skip[0] != '\0' && skip[0] != '0')) {
+    generate_keys(c);
+    // ckks_context.c:141-149: deep contexts get the bootstrapping plaintexts
+    // and keys for full packing right away, unless the program opts out
+    const char* no_bts = std::getenv("RTLIB_DISABLE_BOOTSTRAP_PRECOM");
+    if (!(no_bts != nullptr && no_bts[0] != '\0' && no_bts[0] != '0'))
+      prepare_bootstrap(c, p->_poly_degree / 2);
+  }
   // ckks_context.c:151-154: open the program's weight file when it names one
   RT_DATA_INFO* info = Get_rt_data_info();
   if (info != nullptr) {
@@ -382,7 +396,7 @@ POLY Modswitch(POLY res, POLY poly) {
 // (rns_poly.c:310-404): inverse NTT of the dropped limb(s), centred lift and
 // scaling per remaining limb, forward NTT, combine.  Each step is one launch
 // for all limbs of both polynomials.
-static void rescale_polys(Context* c, int npoly, int64_t* const res[2],
+void fhert_rescale_polys(Context* c, int npoly, int64_t* const res[2],
                           const int64_t* const poly[2], size_t level) {
   const uint32_t n = c->N;
   const int      l = (int)level - 1;
@@ -419,7 +433,7 @@ POLY Rescale(POLY res, POLY poly) {
   FHERT_ASSERT(poly->_is_ntt, "Rescale: coefficient-form input is not supported");
   int64_t*       r[2] = {res->_data, nullptr};
   const int64_t* p[2] = {poly->_data, nullptr};
-  rescale_polys(c, 1, r, p, level);
+  fhert_rescale_polys(c, 1, r, p, level);
   res->_is_ntt     = true;
   res->_num_primes = level - 1;  // Modswitch(res, res)
   return res;
@@ -451,7 +465,7 @@ POLY Decomp(POLY res, POLY poly, uint32_t part) {
   return res;
 }
 
-static void launch_ntt_chunked(Ptr2 in, Ptr2 out, const std::vector<LimbRef>& limbs, bool inverse) {
+static void fhert_launch_ntt_chunked(Ptr2 in, Ptr2 out, const std::vector<LimbRef>& limbs, bool inverse) {
   for (size_t off = 0; off < limbs.size(); off += kMaxLimbs) {
     LimbBatch b;
     b.count = (int)std::min((size_t)kMaxLimbs, limbs.size() - off);
@@ -467,7 +481,7 @@ static void launch_ntt_chunked(Ptr2 in, Ptr2 out, const std::vector<LimbRef>& li
 // complement limbs are written; the digit's own limbs are left to the caller.
 // One inverse-NTT launch, one base-conversion launch and one forward-NTT
 // launch cover all digits.
-static void raise_parts(Context* c, const int64_t* src, bool is_ntt, size_t level,
+void fhert_raise_parts(Context* c, const int64_t* src, bool is_ntt, size_t level,
                         int part_begin, int part_end, int64_t* ext_base, size_t part_stride,
                         int p_limb) {
   const uint32_t n = c->N;
@@ -480,7 +494,7 @@ static void raise_parts(Context* c, const int64_t* src, bool is_ntt, size_t leve
     std::vector<LimbRef> lim;
     for (int i = first; i < last; i++)
       lim.push_back(LimbRef{(uint16_t)i, 0, (uint16_t)i, (uint8_t)i, 0});
-    launch_ntt_chunked(ptr2(src), ptr2(d), lim, true);
+    fhert_launch_ntt_chunked(ptr2(src), ptr2(d), lim, true);
     coeff = d;
   }
   std::vector<LimbRef> out_limbs;
@@ -517,7 +531,7 @@ static void raise_parts(Context* c, const int64_t* src, bool is_ntt, size_t leve
     }
     launch_base_conv(args);
   }
-  if (is_ntt) launch_ntt_chunked(ptr2(ext_base), ptr2(ext_base), out_limbs, false);
+  if (is_ntt) fhert_launch_ntt_chunked(ptr2(ext_base), ptr2(ext_base), out_limbs, false);
 }
 
 POLY Decomp_modup(POLY res, POLY poly, uint32_t part) {
@@ -528,7 +542,7 @@ POLY Decomp_modup(POLY res, POLY poly, uint32_t part) {
   size_t start = (size_t)c->alpha * part;
   FHERT_ASSERT(start < level, "Decomp_modup: digit out of range");
   size_t len = std::min((size_t)c->alpha, level - start);
-  raise_parts(c, poly->_data, poly->_is_ntt, level, (int)part, (int)part + 1, res->_data, 0,
+  fhert_raise_parts(c, poly->_data, poly->_is_ntt, level, (int)part, (int)part + 1, res->_data, 0,
               (int)p_offset(res));
   CUDA_CHECK(cudaMemcpyAsync(res->_data + start * c->N, poly->_data + start * c->N,
                              len * c->N * sizeof(int64_t), cudaMemcpyDeviceToDevice, c->stream));
@@ -546,7 +560,7 @@ POLY Mod_up(POLY res, POLY old_poly, uint32_t part) {
   // place the digit at its own limbs of res, then raise from there
   CUDA_CHECK(cudaMemcpyAsync(res->_data + start * c->N, old_poly->_data,
                              len * c->N * sizeof(int64_t), cudaMemcpyDeviceToDevice, c->stream));
-  raise_parts(c, res->_data, old_poly->_is_ntt, level, (int)part, (int)part + 1, res->_data, 0,
+  fhert_raise_parts(c, res->_data, old_poly->_is_ntt, level, (int)part, (int)part + 1, res->_data, 0,
               (int)p_offset(res));
   res->_is_ntt = old_poly->_is_ntt;
   return res;
@@ -555,7 +569,7 @@ POLY Mod_up(POLY res, POLY old_poly, uint32_t part) {
 // ModDown of one or two extended polynomials of the same level
 // (rns_poly.c:260-308): res[g] = (x[g] - Conv_P->Q(x[g] mod P)) * P^-1, plus
 // add[g] when given.  ext[g] has its special limbs at limb index ext_p_limb.
-static void mod_down_polys(Context* c, int npoly, int64_t* const res[2],
+void fhert_mod_down_polys(Context* c, int npoly, int64_t* const res[2],
                            const int64_t* const ext[2], int ext_p_limb,
                            const int64_t* const add[2], size_t level, bool is_ntt) {
   const uint32_t n = c->N;
@@ -624,7 +638,7 @@ POLY Mod_down(POLY res, POLY poly) {
                "Mod_down: result size not match");
   int64_t*       r[2] = {res->_data, nullptr};
   const int64_t* x[2] = {poly->_data, nullptr};
-  mod_down_polys(c, 1, r, x, (int)p_offset(poly), nullptr, level, poly->_is_ntt);
+  fhert_mod_down_polys(c, 1, r, x, (int)p_offset(poly), nullptr, level, poly->_is_ntt);
   res->_is_ntt = poly->_is_ntt;
   return res;
 }
@@ -807,7 +821,7 @@ CIPHER3 Mul_ciph3(CIPHER3 res, CIPHER a, CIPHER b) {
 // out0/out1 receive level limbs; add0/add1 (optional) are added to them, which
 // folds the "+ c0" of a rotation and the "+ c0, + c1" of a relinearisation
 // into the last kernel.  About a dozen launches regardless of the digit count.
-static void switch_key(Context* c, int64_t* out0, int64_t* out1, const int64_t* in, size_t level,
+void fhert_switch_key(Context* c, int64_t* out0, int64_t* out1, const int64_t* in, size_t level,
                        SW_KEY swk, const int64_t* add0, const int64_t* add1) {
   const uint32_t n     = c->N;
   const int      K     = c->K;
@@ -818,7 +832,7 @@ static void switch_key(Context* c, int64_t* out0, int64_t* out1, const int64_t* 
   CUDA_CHECK(cudaMallocAsync(&buf, (size_t)(parts + 2) * ext_limbs * n * sizeof(int64_t), c->stream));
   int64_t* acc0 = buf + (size_t)parts * ext_limbs * n;
   int64_t* acc1 = acc0 + ext_limbs * n;
-  raise_parts(c, in, true, level, 0, parts, buf, ext_limbs, (int)level);
+  fhert_raise_parts(c, in, true, level, 0, parts, buf, ext_limbs, (int)level);
   InnerArgs args;
   std::memset(&args, 0, sizeof(args));
   args.parts      = parts;
@@ -839,7 +853,7 @@ static void switch_key(Context* c, int64_t* out0, int64_t* out1, const int64_t* 
   int64_t*       r[2] = {out0, out1};
   const int64_t* x[2] = {acc0, acc1};
   const int64_t* a[2] = {add0, add1};
-  mod_down_polys(c, 2, r, x, (int)level, a, level, true);
+  fhert_mod_down_polys(c, 2, r, x, (int)level, a, level, true);
   CUDA_CHECK(cudaFreeAsync(buf, c->stream));
 }
 
@@ -848,7 +862,7 @@ CIPHER Relin(CIPHER res, CIPHER3 ciph) {
   Context* c     = ctx();
   size_t   level = ciph->_c2_poly._num_primes;
   init_ciph(res, c->N, level, 0, ciph->_scaling_factor, ciph->_sf_degree, ciph->_slots);
-  switch_key(c, res->_c0_poly._data, res->_c1_poly._data, ciph->_c2_poly._data, level,
+  fhert_switch_key(c, res->_c0_poly._data, res->_c1_poly._data, ciph->_c2_poly._data, level,
              Swk(false, 0), ciph->_c0_poly._data, ciph->_c1_poly._data);
   return res;
 }
@@ -874,7 +888,7 @@ CIPHER Rescale_ciph(CIPHER res, CIPHER ciph) {
             ciph->_scaling_factor / Get_default_sc(), ciph->_sf_degree - 1, ciph->_slots);
   int64_t*       r[2] = {res->_c0_poly._data, res->_c1_poly._data};
   const int64_t* p[2] = {ciph->_c0_poly._data, ciph->_c1_poly._data};
-  rescale_polys(c, 2, r, p, level);
+  fhert_rescale_polys(c, 2, r, p, level);
   res->_c0_poly._num_primes = res->_c1_poly._num_primes = level - 1;
   return res;
 }
@@ -886,7 +900,7 @@ static CIPHER rotate_with_key(CIPHER res, CIPHER ciph, int32_t rot_idx, uint32_t
   size_t   words = level * c->N;
   int64_t* t     = nullptr;
   CUDA_CHECK(cudaMallocAsync(&t, 2 * words * sizeof(int64_t), c->stream));
-  switch_key(c, t, t + words, ciph->_c1_poly._data, level, Swk(true, rot_idx),
+  fhert_switch_key(c, t, t + words, ciph->_c1_poly._data, level, Swk(true, rot_idx),
              ciph->_c0_poly._data, nullptr);
   if (res != ciph)
     init_ciph(res, c->N, level, 0, ciph->_scaling_factor, ciph->_sf_degree, ciph->_slots);

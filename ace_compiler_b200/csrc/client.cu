@@ -277,6 +277,20 @@ void generate_keys(Context* c) {
   CUDA_CHECK(cudaStreamSynchronize(c->stream));
 }
 
+// bootstrap.c:1199-1231: keys for the rotations of the linear transforms, in
+// ascending order of rotation, then the conjugation key
+void generate_bootstrap_keys(Context* c, const std::vector<int32_t>& rotations) {
+  FHERT_ASSERT(c->sk_s._data != nullptr, "bootstrap keys need the secret key of this context");
+  for (int32_t r : rotations) {
+    uint32_t k = auto_index_for(c, r);
+    if (c->keys.count(k)) continue;
+    generate_rotation_key(c, k, false);
+  }
+  uint32_t conj = 2 * c->N - 1;
+  if (!c->keys.count(conj)) generate_rotation_key(c, conj, true);
+  CUDA_CHECK(cudaStreamSynchronize(c->stream));
+}
+
 void free_keys(Context* c) {
   for (POLYNOMIAL* p : {&c->sk_s, &c->sk_ntt, &c->pk._p0, &c->pk._p1})
     if (p->_data) Free_poly_data(p);

@@ -96,33 +96,85 @@ void embedding(Context* c, std::vector<cplx>& v) {
   v.swap(res);
 }
 
-void init_plain(Context* c, PLAIN plain, size_t level, double scale, uint32_t sf_degree) {
+void init_plain(Context* c, PLAIN plain, size_t level, double scale, uint32_t sf_degree,
+                uint32_t slots = 0, size_t num_p = 0) {
   POLY p = &plain->_poly;
-  if (p->_data == nullptr || p->_num_alloc_primes < level) {
+  // special limbs sit at the end of the allocation, so an extended plaintext
+  // needs storage of exactly level + K limbs
+  if (p->_data == nullptr || (num_p ? p->_num_alloc_primes != level + num_p
+                                    : p->_num_alloc_primes < level)) {
     Free_poly_data(p);
-    Alloc_poly_data(p, c->N, level, 0);
+    Alloc_poly_data(p, c->N, level, num_p);
   } else {
     p->_num_primes   = level;
-    p->_num_primes_p = 0;
+    p->_num_primes_p = num_p;
   }
   plain->_scaling_factor = scale;
   plain->_sf_degree      = sf_degree;
-  plain->_slots          = c->N / 2;
+  plain->_slots          = slots ? slots : c->N / 2;
 }
 
-LimbBatch q_batch(size_t level) {
+// level Q limbs, then num_p special limbs stored right behind them
+LimbBatch q_batch(size_t level, size_t num_p = 0, int first_p_prime = 0) {
   LimbBatch b;
-  b.count = (int)level;
+  b.count = (int)(level + num_p);
   for (size_t i = 0; i < level; i++)
     b.limb[i] = LimbRef{(uint16_t)i, (uint16_t)i, (uint16_t)i, (uint8_t)i, 0};
+  for (size_t k = 0; k < num_p; k++) {
+    uint16_t at = (uint16_t)(level + k);
+    b.limb[level + k] = LimbRef{at, at, at, (uint8_t)(first_p_prime + k), 0};
+  }
   return b;
 }
 
-// ckks/src/encoder.c:234-325 with slots = N/2 and no special limbs
+}  // namespace
+
+namespace fhert {
+
+// ckks/src/encoder.c:473-520: residues of one real value at the given scale,
+// on level Q limbs followed by num_p special limbs
+std::vector<int64_t> encode_value(Context* c, double value, uint32_t level, double scale,
+                                  uint32_t num_p) {
+  FHERT_ASSERT(level > 0 && level <= (uint32_t)c->L, "level should not be larger than q_cnt");
+  FHERT_ASSERT(num_p == 0 || num_p == (uint32_t)c->K, "invalid p cnt");
+  int32_t log_scale  = (int32_t)std::log2(std::fabs(value * scale));
+  int32_t log_valid  = log_scale <= 61 ? log_scale : 61;
+  int32_t log_approx = log_scale - log_valid;
+  double  scaled     = value / std::pow(2, log_approx) * scale;
+  int64_t val_int    = (int64_t)scaled;
+  std::vector<int64_t> res(level + num_p);
+  for (uint32_t i = 0; i < level + num_p; i++) {
+    int64_t q = (int64_t)c->primes[i < level ? i : c->L + (i - level)], r = val_int % q;
+    res[i] = r < 0 ? r + q : r;
+  }
+  if (log_approx > 0) {
+    // scale back up by 2^log_approx in steps of at most 61 then 60 bits
+    for (uint32_t i = 0; i < level; i++) {
+      u64     q = c->primes[i];
+      int32_t left = log_approx, step = left <= 61 ? left : 61;
+      u64     f = (1ull << step) % q;
+      left -= step;
+      while (left > 0) {
+        step = left <= 60 ? left : 60;
+        f    = mulmod(f, (1ull << step) % q, q);
+        left -= step;
+      }
+      res[i] = (int64_t)mulmod((u64)res[i], f, q);
+    }
+  }
+  return res;
+}
+
+// ckks/src/encoder.c:234-325; slots = 0 means N/2, num_p = K also fills the
+// special limbs (the plaintexts of the bootstrapping linear transforms)
 void encode_vector(Context* c, PLAIN plain, std::vector<cplx>& values, uint32_t sf_degree,
-                   uint32_t level) {
+                   uint32_t level, uint32_t slots, uint32_t num_p) {
   ensure_fft_tables(c);
-  const uint32_t n = c->N, slots = n / 2;
+  const uint32_t n = c->N;
+  if (slots == 0) slots = n / 2;
+  FHERT_ASSERT(slots <= n / 2 && (slots & (slots - 1)) == 0, " slot size > N/2 ");
+  FHERT_ASSERT(num_p == 0 || num_p == (uint32_t)c->K, "invalid p cnt");
+  const uint32_t gap = n / (slots * 2);
   if (level == 0) level = c->L;
   FHERT_ASSERT(level <= (uint32_t)c->L, "level should not be larger than mul_depth + 1");
   FHERT_ASSERT(values.size() <= slots, "slot size is too small");
@@ -130,14 +182,14 @@ void encode_vector(Context* c, PLAIN plain, std::vector<cplx>& values, uint32_t 
   const double delta = std::pow(2.0, (double)c->sf_bits);
   values.resize(slots, cplx(0, 0));
   embedding_inv(c, values);
-  std::vector<int64_t> msg(n);
+  std::vector<int64_t> msg(n, 0);
   for (uint32_t i = 0; i < slots; i++) {
     double  re = values[i].real() * delta + 0.5, im = values[i].imag() * delta + 0.5;
     int64_t r = std::llround(re), m = std::llround(im);
-    msg[i]         = r < 0 ? kMax64 + r : r;
-    msg[i + slots] = m < 0 ? kMax64 + m : m;
+    msg[(size_t)i * gap]           = r < 0 ? kMax64 + r : r;
+    msg[(size_t)(i + slots) * gap] = m < 0 ? kMax64 + m : m;
   }
-  init_plain(c, plain, level, std::pow(delta, (double)sf_degree), sf_degree);
+  init_plain(c, plain, level, std::pow(delta, (double)sf_degree), sf_degree, slots, num_p);
   int64_t* d_msg = nullptr;
   u64*     d_pow = nullptr;
   CUDA_CHECK(cudaMallocAsync(&d_msg, n * sizeof(int64_t), c->stream));
@@ -156,7 +208,7 @@ void encode_vector(Context* c, PLAIN plain, std::vector<cplx>& values, uint32_t 
     CUDA_CHECK(cudaMemcpyAsync(d_pow, powp.data(), powp.size() * sizeof(u64),
                                cudaMemcpyHostToDevice, c->stream));
   }
-  launch_encode_split(plain->_poly._data, d_msg, d_pow, q_batch(level));
+  launch_encode_split(plain->_poly._data, d_msg, d_pow, q_batch(level, num_p, c->L));
   CUDA_CHECK(cudaStreamSynchronize(c->stream));  // msg and powp live on the host stack
   CUDA_CHECK(cudaFreeAsync(d_msg, c->stream));
   if (d_pow) CUDA_CHECK(cudaFreeAsync(d_pow, c->stream));
@@ -164,36 +216,16 @@ void encode_vector(Context* c, PLAIN plain, std::vector<cplx>& values, uint32_t 
   Conv_poly2ntt_inplace(&plain->_poly);
 }
 
+}  // namespace fhert
+
+namespace {
+
 // ckks/src/encoder.c:473-575: one value on every coefficient of every limb
 void encode_scalar(Context* c, PLAIN plain, double value, uint32_t sf_degree, uint32_t level) {
   if (level == 0) level = c->L;
   const double delta = std::pow(2.0, (double)c->sf_bits), scale = std::pow(delta, sf_degree);
   init_plain(c, plain, level, scale, sf_degree);
-  int32_t log_scale  = (int32_t)std::log2(std::fabs(value * scale));
-  int32_t log_valid  = log_scale <= 61 ? log_scale : 61;
-  int32_t log_approx = log_scale - log_valid;
-  double  scaled     = value / std::pow(2, log_approx) * scale;
-  int64_t val_int    = (int64_t)scaled;
-  std::vector<int64_t> res(level);
-  for (uint32_t i = 0; i < level; i++) {
-    int64_t q = (int64_t)c->primes[i], r = val_int % q;
-    res[i] = r < 0 ? r + q : r;
-  }
-  if (log_approx > 0) {
-    // scale back up by 2^log_approx in steps of at most 61 then 60 bits
-    for (uint32_t i = 0; i < level; i++) {
-      u64     q = c->primes[i];
-      int32_t left = log_approx, step = left <= 61 ? left : 61;
-      u64     f = (1ull << step) % q;
-      left -= step;
-      while (left > 0) {
-        step = left <= 60 ? left : 60;
-        f    = mulmod(f, (1ull << step) % q, q);
-        left -= step;
-      }
-      res[i] = (int64_t)mulmod((u64)res[i], f, q);
-    }
-  }
+  std::vector<int64_t> res = encode_value(c, value, level, scale, 0);
   // fill: zero the limb, then add the scalar
   POLY p = &plain->_poly;
   CUDA_CHECK(cudaMemsetAsync(p->_data, 0, (size_t)level * c->N * sizeof(int64_t), c->stream));

@@ -505,6 +505,7 @@ Context* create_context(const CKKS_PARAMS* p) {
 void destroy_context() {
   Context* c = g_ctx;
   if (!c) return;
+  free_bootstrap(c);
   free_keys(c);
   release_prng();
   cudaStreamSynchronize(c->stream);

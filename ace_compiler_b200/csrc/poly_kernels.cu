@@ -57,6 +57,25 @@ ew_kernel(Ptr2 res, Ptr2 a, Ptr2 b, u64 scalar, LimbBatch batch,
   }
 }
 
+// one reduced scalar per limb of the batch, passed by value
+// (rns_poly.c Scalars_integer_add_poly / Scalars_integer_multiply_poly)
+struct ScalarList {
+  u64 v[kMaxLimbs];
+};
+
+template <bool MUL>
+__global__ void __launch_bounds__(kThreads)
+ew_scalars_kernel(Ptr2 res, Ptr2 a, ScalarList sc, LimbBatch batch,
+                  const DevModulus* __restrict__ mods, uint32_t n) {
+  const LimbRef    lr = batch.limb[blockIdx.y];
+  const DevModulus m  = mods[lr.prime];
+  const u64        s  = sc.v[blockIdx.y];
+  const u64*       pa = sel_a(a, lr, n);
+  u64*             pr = sel_d(res, lr, n);
+  for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads)
+    pr[i] = MUL ? mul_mod(pa[i], s, m) : add_mod(pa[i], s, m.q);
+}
+
 // ---- automorphism in NTT form: a pure gather (hal.c:123-138) ----------------
 
 __global__ void __launch_bounds__(kThreads)
@@ -335,6 +354,18 @@ void launch_elementwise(EwOp op, Ptr2 res, Ptr2 a, Ptr2 b, int64_t scalar,
     EW_CASE(EW_MUL_SCALAR)
   }
 #undef EW_CASE
+  after_launch(c, KID_ELEMENTWISE, batch.count);
+}
+
+void launch_scalars(bool mul, Ptr2 res, Ptr2 a, const u64* per_limb, const LimbBatch& batch) {
+  if (batch.count == 0) return;
+  Context* c = ctx();
+  ScalarList sc;
+  for (int i = 0; i < batch.count; i++) sc.v[i] = per_limb[i];
+  prof_before(KID_ELEMENTWISE);
+  dim3 g = grid_for(c->N, 2, batch.count);
+  if (mul) ew_scalars_kernel<true><<<g, kThreads, 0, c->stream>>>(res, a, sc, batch, c->d_mod, c->N);
+  else ew_scalars_kernel<false><<<g, kThreads, 0, c->stream>>>(res, a, sc, batch, c->d_mod, c->N);
   after_launch(c, KID_ELEMENTWISE, batch.count);
 }
 

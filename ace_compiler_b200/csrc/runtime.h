@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <complex>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -131,6 +132,8 @@ struct Context {
   // encoder tables (util/src/ntt.c:562-590): 2N-th complex roots, powers of 5
   std::vector<double>   fft_rou_re, fft_rou_im;
   std::vector<uint32_t> fft_rot_group;
+  // bootstrapping precomputation per slot count, owned by bootstrap.cu
+  void* bootstrap = nullptr;
 
   cudaStream_t stream = nullptr;
   uint64_t     launches = 0;
@@ -177,6 +180,7 @@ void sample_triangle(int64_t* out, size_t n);
 // ---- client.cu ----
 void generate_keys(Context* c);
 void free_keys(Context* c);
+void generate_bootstrap_keys(Context* c, const std::vector<int32_t>& rotations);
 SWITCH_KEY* key_slot(Context* c, uint32_t key_id, bool create);
 // msg[N] (signed values, negatives stored as Max64 + x) -> residues per limb,
 // times scale_pow[prime] when given                       (crt.c:1153-1221)
@@ -184,6 +188,27 @@ void launch_encode_split(int64_t* poly, const int64_t* msg, const u64* scale_pow
                          const LimbBatch& batch);
 // small signed samples (-1, 0, 1) -> residues per limb (crt.c:1168-1172)
 void launch_small_to_rns(int64_t* poly, const int64_t* vals, const LimbBatch& batch);
+
+// ---- api.cu (batch builders shared with the bootstrapping code) ----
+LimbBatch poly_batch(Context* c, POLY res, POLY a, POLY b, size_t level, size_t num_p);
+LimbBatch both_polys(const LimbBatch& one);
+void      ensure_poly(POLY res, uint32_t degree, size_t num_q, size_t num_p);
+
+// ---- client_api.cu ----
+// encode at sf_degree and level; slots = 0 means N/2, num_p = K also fills
+// the special limbs (stored right behind the level Q limbs)
+void encode_vector(Context* c, PLAIN plain, std::vector<std::complex<double>>& values,
+                   uint32_t sf_degree, uint32_t level, uint32_t slots = 0, uint32_t num_p = 0);
+// residues of one real value at the given scale on level Q limbs then num_p
+// special limbs
+std::vector<int64_t> encode_value(Context* c, double value, uint32_t level, double scale,
+                                  uint32_t num_p);
+
+// ---- bootstrap.cu ----
+// builds the linear-transform plaintexts and the rotation / conjugation keys
+// for `slots` (0 = N/2) when the context is deep enough (ckks_context.c:239-262)
+void prepare_bootstrap(Context* c, uint32_t slots);
+void free_bootstrap(Context* c);
 
 // ---- context.cu ----
 Context* create_context(const CKKS_PARAMS* p);
@@ -200,6 +225,9 @@ enum EwOp { EW_ADD, EW_SUB, EW_MUL, EW_MULADD, EW_ADD_SCALAR, EW_MUL_SCALAR };
 // res[dst] = a[a] op b[b]   (EW_MULADD: res[dst] += a*b; scalar ops ignore b)
 void launch_elementwise(EwOp op, Ptr2 res, Ptr2 a, Ptr2 b, int64_t scalar,
                         const LimbBatch& batch);
+// res[dst] = a[a] + per_limb[k] (or * when mul) for the k-th limb of the batch;
+// the scalars are residues already reduced modulo the limb's prime
+void launch_scalars(bool mul, Ptr2 res, Ptr2 a, const u64* per_limb, const LimbBatch& batch);
 // res[dst][i] = val[a][table[i]]
 void launch_automorphism(Ptr2 res, Ptr2 val, const uint32_t* table, const LimbBatch& batch);
 // res[dst] = val[a] * consts[prime]
@@ -270,3 +298,21 @@ void launch_inner_product(const InnerArgs& args);
 void launch_mod_raise(int64_t* res, const int64_t* src, const LimbBatch& batch);
 
 }  // namespace fhert
+
+// ---- api.cu: multi-polynomial building blocks shared with bootstrap.cu ------
+extern "C" {
+// ModUp of digits [part_begin, part_end) of a level-`level` polynomial at src:
+// digit j lands at ext_base + (j - part_begin) * part_stride limbs, Q limbs at
+// limb 0.., special limbs at limb p_limb..; the digit's own limbs are not written
+void fhert_raise_parts(fhert::Context* c, const int64_t* src, bool is_ntt, size_t level,
+                       int part_begin, int part_end, int64_t* ext_base, size_t part_stride,
+                       int p_limb);
+// ModDown of one or two extended polynomials (special limbs at ext_p_limb),
+// optionally adding add[g] to the result
+void fhert_mod_down_polys(fhert::Context* c, int npoly, int64_t* const res[2],
+                          const int64_t* const ext[2], int ext_p_limb,
+                          const int64_t* const add[2], size_t level, bool is_ntt);
+// Rescale of one or two NTT-form polynomials from level to level - 1
+void fhert_rescale_polys(fhert::Context* c, int npoly, int64_t* const res[2],
+                         const int64_t* const poly[2], size_t level);
+}

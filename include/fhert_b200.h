@@ -374,6 +374,23 @@ CIPHER  Rescale_ciph(CIPHER res, CIPHER ciph);          /* evaluator.c:344 */
 CIPHER  Rotate_ciph(CIPHER res, CIPHER ciph, int32_t rot_idx); /* evaluator.c:503-530 */
 CIPHER  Conjugate_ciph(CIPHER res, CIPHER ciph);        /* evaluator.c:568 */
 
+/* Bootstrapping (ant/ckks/src/cipher.c:565-583, bootstrap.c:1549-1830): raises
+ * an exhausted ciphertext back to level_after_bts levels (0 = as many as the
+ * context allows) with the reference's level budget {3, 3}, cosine series and
+ * double-angle count.  Prepare_context builds the plaintexts and keys for
+ * full packing when the context is deeper than the bootstrap itself, unless
+ * RTLIB_DISABLE_BOOTSTRAP_PRECOM is set; other slot counts are prepared on
+ * first use (context/src/ckks_context.c:239-262). */
+CIPHER Bootstrap(CIPHER res, CIPHER ciph, uint32_t level_after_bts);
+void   Bootstrap_precom(uint32_t num_slots);
+/* rotation amounts whose keys bootstrapping at this slot count uses (ascending;
+ * the conjugation key comes on top); returns how many there are */
+size_t Fhert_bootstrap_rotations(uint32_t slots, int32_t* out, size_t cap);
+/* host copy of one linear-transform plaintext (its Q limbs, then its K special
+ * limbs); returns the Q limb count, 0 when that diagonal does not exist */
+size_t Fhert_export_bootstrap_plain(uint32_t slots, int encoding, uint32_t stage, uint32_t index,
+                                    int64_t* host);
+
 /* ------------------------------------------------------------------------ */
 /* Program driver  (include/common/rt_api.h, ant/ckks/src/rtlib.c:164-244,   */
 /* common/src/tensor.c, common/src/rt_stat.c)                                */

@@ -331,3 +331,39 @@ void Ref_decrypt_decode(const int64_t* c0, const int64_t* c1, size_t level, uint
   free(t0);
   free(t1);
 }
+
+//! Bootstrap (cipher.c:581): in = level limbs at scaling degree 1 with all
+//! N/2 slots; returns the output level, out0/out1 must hold Get_q_cnt() limbs
+size_t Ref_bootstrap(const int64_t* c0, const int64_t* c1, size_t level, uint32_t slots,
+                     uint32_t level_after, int64_t* out0, int64_t* out1) {
+  CIPHERTEXT in, out;
+  Wrap_ciph(&in, (int64_t*)c0, (int64_t*)c1, level, Get_default_sc(), 1);
+  in._slots = slots;
+  memset(&out, 0, sizeof(out));
+  Bootstrap(&out, &in, level_after);
+  size_t out_level = Poly_level(Get_c0(&out));
+  Export_ciph(&out, out0, out1);
+  Free_poly_data(Get_c0(&out));
+  Free_poly_data(Get_c1(&out));
+  return out_level;
+}
+
+//! One plaintext of the bootstrapping linear transforms for N/2 slots:
+//! writes its Q limbs then its special limbs, returns the Q limb count
+//! (0 when that diagonal does not exist)
+size_t Ref_bootstrap_plain(int encoding, uint32_t stage, uint32_t index, int64_t* out) {
+  CKKS_BTS_CTX*    bts    = Get_bts_ctx((CKKS_EVALUATOR*)Eval());
+  CKKS_BTS_PRECOM* precom = Get_bts_precom(bts, Degree() / 2);
+  if (precom == NULL) return 0;
+  VL_VL_PLAIN* all = encoding ? Get_u0hatt_pre_fft(precom) : Get_u0_pre_fft(precom);
+  if (stage >= LIST_LEN(all)) return 0;
+  VALUE_LIST* row = Get_vl_value_at(all, stage);
+  if (index >= LIST_LEN(row)) return 0;
+  PLAINTEXT* pt = (PLAINTEXT*)Get_ptr_value_at(row, index);
+  if (pt == NULL) return 0;
+  POLYNOMIAL* p = Get_plain_poly(pt);
+  size_t      n = Degree();
+  memcpy(out, Get_poly_coeffs(p), Poly_level(p) * n * sizeof(int64_t));
+  memcpy(out + Poly_level(p) * n, Get_p_coeffs(p), Num_p(p) * n * sizeof(int64_t));
+  return Poly_level(p);
+}
