@@ -149,14 +149,14 @@ void Finalize_context(void) {
   destroy_context();
 }
 
-uint32_t Degree(void) { return ctx()->N; }
-size_t   Get_q_cnt(void) { return ctx()->L; }
-size_t   Get_p_cnt(void) { return ctx()->K; }
+uint32_t Degree(void) { return ctx_noflush()->N; }
+size_t   Get_q_cnt(void) { return ctx_noflush()->L; }
+size_t   Get_p_cnt(void) { return ctx_noflush()->K; }
 size_t   Get_q_parts(void) { return ctx()->dnum; }
 size_t   Get_part_size(void) { return ctx()->alpha; }
-MODULUS* Q_modulus(void) { return ctx()->moduli.data(); }
-MODULUS* P_modulus(void) { return ctx()->moduli.data() + ctx()->L; }
-double   Get_default_sc(void) { return std::pow(2.0, (double)ctx()->sf_bits); }
+MODULUS* Q_modulus(void) { return ctx_noflush()->moduli.data(); }
+MODULUS* P_modulus(void) { return ctx_noflush()->moduli.data() + ctx_noflush()->L; }
+double   Get_default_sc(void) { return std::pow(2.0, (double)ctx_noflush()->sf_bits); }
 
 void Fhert_get_primes(int64_t* primes) {
   Context* c = ctx();
@@ -253,6 +253,8 @@ int64_t* Coeffs(POLY poly, uint32_t limb, uint32_t degree) {
 void Set_coeffs(POLY poly, uint32_t limb, uint32_t degree, int64_t* src) {
   int64_t* dst = poly->_data + (size_t)limb * degree;
   if (dst == src) return;
+  Context* c = ctx_noflush();
+  if (degree == c->N && hw_record(c, HW_COPY, dst, src, nullptr, nullptr, 0, 0)) return;
   CUDA_CHECK(cudaMemcpyAsync(dst, src, (size_t)degree * sizeof(int64_t),
                              cudaMemcpyDeviceToDevice, ctx()->stream));
 }
@@ -286,9 +288,11 @@ size_t   Fhert_profile_end(char* buf, size_t cap) { return prof_end(buf, cap); }
 
 static int64_t* hw_binary(EwOp op, int64_t* res, int64_t* a, int64_t* b, int64_t s, MODULUS* m,
                           uint32_t degree) {
-  Context* c = ctx();
+  Context* c = ctx_noflush();
   FHERT_ASSERT(degree == c->N, "degree mismatch");
-  launch_elementwise(op, ptr2(res), ptr2(a), ptr2(b), s, single(prime_index_of(c, m)));
+  int prime = prime_index_of(c, m);
+  if (hw_record(c, (HwKind)op, res, a, b, nullptr, s, prime)) return res;
+  launch_elementwise(op, ptr2(res), ptr2(a), ptr2(b), s, single(prime));
   return res;
 }
 
@@ -311,9 +315,11 @@ int64_t* Hw_modmul_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint3
   return hw_binary(EW_MUL_SCALAR, res, a, a, s, m, degree);
 }
 int64_t* Hw_rotate(int64_t* res, int64_t* val, int64_t* order, MODULUS* m, uint32_t degree) {
-  Context* c = ctx();
+  Context* c = ctx_noflush();
   FHERT_ASSERT(degree == c->N, "degree mismatch");
   FHERT_ASSERT(res != val, "Hw_rotate cannot work in place");
+  const uint32_t* table = reinterpret_cast<const uint32_t*>(order);
+  if (hw_record(c, HW_ROTATE, res, val, nullptr, table, 0, 0)) return res;
   launch_automorphism(ptr2(res), ptr2(val), reinterpret_cast<const uint32_t*>(order), single(0));
   return res;
 }

@@ -246,6 +246,26 @@ void Fhert_seed(const uint32_t seed[16], uint64_t counter, int64_t fake_time_us)
   seed_prng(seed, counter, fake_time_us);
 }
 
+// ckks/src/cipher.c:172-186: would msg still fit the modulus at the
+// ciphertext's level and scale
+bool Within_value_range(CIPHER ciph, double* msg, uint32_t len) {
+  Context* c     = ctx();
+  uint32_t slots = ciph->_slots;
+  FHERT_ASSERT(len <= slots, "length of msg should less than slots");
+  ensure_fft_tables(c);
+  std::vector<cplx> v(slots, cplx(0, 0));
+  for (uint32_t i = 0; i < len; i++) v[i] = cplx(msg[i], 0.0);
+  embedding_inv(c, v);
+  double top = 0.0;
+  for (auto& x : v) {
+    top = std::max(top, std::fabs(x.real() * ciph->_scaling_factor));
+    top = std::max(top, std::fabs(x.imag() * ciph->_scaling_factor));
+  }
+  int32_t bits  = (int32_t)std::log2(std::max(top, 2.2250738585072014e-308)) + 1;
+  int32_t valid = (int32_t)c->q0_bits + ((int32_t)ciph->_c0_poly._num_primes - 1) * (int32_t)c->sf_bits;
+  return bits < valid;
+}
+
 void Free_plain_data(PLAIN plain) { Free_poly_data(&plain->_poly); }
 
 void Encode_double(PLAIN plain, double* input, size_t len, uint32_t sc_degree, uint32_t level) {

@@ -15,6 +15,11 @@ static Context* g_ctx = nullptr;
 
 Context* ctx() {
   FHERT_ASSERT(g_ctx != nullptr, "no context: call Prepare_context first");
+  if (g_ctx->hw_pending) hw_replay(g_ctx);  // recorded per-limb operations run first
+  return g_ctx;
+}
+Context* ctx_noflush() {
+  FHERT_ASSERT(g_ctx != nullptr, "no context: call Prepare_context first");
   return g_ctx;
 }
 Context* ctx_or_null() { return g_ctx; }
@@ -505,6 +510,7 @@ Context* create_context(const CKKS_PARAMS* p) {
 void destroy_context() {
   Context* c = g_ctx;
   if (!c) return;
+  hw_release(c);
   free_bootstrap(c);
   free_keys(c);
   release_prng();

@@ -1,0 +1,273 @@
+// Deferred execution of the per-limb vector entry points (Hw_modadd,
+// Hw_modmul, Hw_rotate ...).
+//
+// A compiled program calls these once per RNS limb from inside its own loops
+// (hal/src/hal.c:15-138 are the CPU versions), tens of thousands of times per
+// operator.  Launching one kernel per call would leave the GPU idle between
+// half-megabyte launches, so the calls are only recorded.  Every other entry
+// point of the library reaches the context through ctx(), which first replays
+// what was recorded: the recorded operations are ordered by data dependence
+// into waves, and each wave runs as one launch per operation kind covering up
+// to kHwItems limbs.
+//
+// Dependences are tracked per limb address (operands are whole limbs, either
+// identical or disjoint).  A scratch limb that a program reuses for every
+// limb of a loop (the "tmp = key * digit; acc += tmp" idiom) would chain all
+// iterations together, so a value written over a limb that still has readers
+// waiting is given a fresh scratch limb instead (renaming); the last value of
+// such a limb is copied to its real address at the end of the replay.
+#include <algorithm>
+#include <unordered_map>
+#include <vector>
+
+#include "runtime.h"
+
+namespace fhert {
+
+namespace {
+
+constexpr int kThreads  = 256;
+constexpr int kHwItems  = 256;   // limbs per launch
+constexpr int kArena    = 64;    // scratch limbs per allocation
+constexpr int kMaxNodes = 8192;  // replay at the latest after this many calls
+
+struct HwItem {
+  u64*            dst;
+  const u64*      a;
+  const u64*      b;
+  const uint32_t* table;
+  int64_t         scalar;
+  uint32_t        prime;
+};
+
+struct HwLaunch {
+  int    count;
+  HwItem item[kHwItems];
+};
+
+template <int KIND>
+__global__ void __launch_bounds__(kThreads)
+hw_batch_kernel(const __grid_constant__ HwLaunch launch, const DevModulus* __restrict__ mods,
+                uint32_t n) {
+  const HwItem&    it = launch.item[blockIdx.y];
+  const DevModulus m  = mods[it.prime];
+  u64              sc = 0;
+  if (KIND == HW_ADD_SCALAR || KIND == HW_MUL_SCALAR) {
+    int64_t s = it.scalar % (int64_t)m.q;
+    sc        = s < 0 ? (u64)(s + (int64_t)m.q) : (u64)s;
+  }
+  for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads) {
+    u64 r;
+    if (KIND == HW_ADD) r = add_mod(it.a[i], it.b[i], m.q);
+    else if (KIND == HW_SUB) r = sub_mod(it.a[i], it.b[i], m.q);
+    else if (KIND == HW_MUL) r = mul_mod(it.a[i], it.b[i], m);
+    else if (KIND == HW_MULADD) r = add_mod(it.dst[i], mul_mod(it.a[i], it.b[i], m), m.q);
+    else if (KIND == HW_ADD_SCALAR) r = add_mod(it.a[i], sc, m.q);
+    else if (KIND == HW_MUL_SCALAR) r = mul_mod(it.a[i], sc, m);
+    else if (KIND == HW_ROTATE) r = it.a[__ldg(it.table + i)];
+    else r = it.a[i];
+    it.dst[i] = r;
+  }
+}
+
+struct Node {
+  HwKind kind;
+  HwItem item;
+  int    level;
+  bool   dead;
+};
+
+struct Version {  // the newest value of one limb address
+  u64* phys;      // where that value lives (the address itself or a scratch limb)
+  int  writer;    // node that produces it, -1 = already in memory
+  int  writer_level;
+  int  readers;   // recorded operations that read it
+};
+
+struct Usage {  // per physical limb: the latest waves that touch it
+  int read_level  = 0;
+  int write_level = 0;
+};
+
+}  // namespace
+
+struct HwQueue {
+  std::vector<Node>                   nodes;
+  std::unordered_map<u64*, Version>   versions;  // by logical address
+  std::unordered_map<u64*, Usage>     usage;     // by physical address
+  std::vector<u64*>                   arenas;
+  int                                 arena_used = kArena;
+  int                                 max_level  = 0;
+  bool                                replaying  = false;
+  bool                                eager      = false;
+};
+
+namespace {
+
+HwQueue* queue_of(Context* c) {
+  if (c->hw_queue == nullptr) {
+    HwQueue* q = new HwQueue();
+    const char* e = std::getenv("FHERT_EAGER_HW");
+    q->eager      = e != nullptr && e[0] != '\0' && e[0] != '0';
+    c->hw_queue   = q;
+  }
+  return c->hw_queue;
+}
+
+u64* scratch_limb(Context* c, HwQueue* q) {
+  if (q->arena_used == kArena) {
+    u64* p = nullptr;
+    CUDA_CHECK(cudaMallocAsync(&p, (size_t)kArena * c->N * sizeof(u64), c->stream));
+    q->arenas.push_back(p);
+    q->arena_used = 0;
+  }
+  return q->arenas.back() + (size_t)(q->arena_used++) * c->N;
+}
+
+Version& version_of(HwQueue* q, u64* addr) {
+  auto it = q->versions.find(addr);
+  if (it == q->versions.end()) it = q->versions.emplace(addr, Version{addr, -1, 0, 0}).first;
+  return it->second;
+}
+
+void run_wave(Context* c, HwKind kind, const std::vector<const Node*>& wave) {
+  for (size_t off = 0; off < wave.size(); off += kHwItems) {
+    HwLaunch l;
+    l.count = (int)std::min<size_t>(kHwItems, wave.size() - off);
+    for (int i = 0; i < l.count; i++) l.item[i] = wave[off + i]->item;
+    dim3 grid((c->N + kThreads * 2 - 1) / (kThreads * 2), l.count);
+#define HW_CASE(K)                                                                      \
+  case K:                                                                               \
+    hw_batch_kernel<K><<<grid, kThreads, 0, c->stream>>>(l, c->d_mod, c->N);            \
+    break;
+    switch (kind) {
+      HW_CASE(HW_ADD)
+      HW_CASE(HW_SUB)
+      HW_CASE(HW_MUL)
+      HW_CASE(HW_MULADD)
+      HW_CASE(HW_ADD_SCALAR)
+      HW_CASE(HW_MUL_SCALAR)
+      HW_CASE(HW_ROTATE)
+      HW_CASE(HW_COPY)
+    }
+#undef HW_CASE
+    c->launches++;
+    c->hw_batched_limbs += l.count;
+    CUDA_CHECK(cudaGetLastError());
+  }
+}
+
+}  // namespace
+
+void hw_replay(Context* c) {
+  HwQueue* q = c->hw_queue;
+  if (q == nullptr || q->nodes.empty() || q->replaying) return;
+  q->replaying = true;
+  std::vector<const Node*> wave;
+  std::vector<std::vector<const Node*>> by_level(q->max_level + 1);
+  for (const Node& nd : q->nodes)
+    if (!nd.dead) by_level[nd.level].push_back(&nd);
+  for (int level = 1; level <= q->max_level; level++) {
+    for (int kind = 0; kind <= (int)HW_COPY; kind++) {
+      wave.clear();
+      for (const Node* nd : by_level[level])
+        if (nd->kind == (HwKind)kind) wave.push_back(nd);
+      if (!wave.empty()) run_wave(c, (HwKind)kind, wave);
+    }
+  }
+  // values that ended up in scratch limbs go home
+  std::vector<Node> home;
+  for (auto& kv : q->versions) {
+    if (kv.second.phys == kv.first) continue;
+    Node nd{};
+    nd.kind      = HW_COPY;
+    nd.item.dst  = kv.first;
+    nd.item.a    = kv.second.phys;
+    nd.item.prime = 0;
+    home.push_back(nd);
+  }
+  if (!home.empty()) {
+    wave.clear();
+    for (const Node& nd : home) wave.push_back(&nd);
+    run_wave(c, HW_COPY, wave);
+  }
+  for (u64* p : q->arenas) CUDA_CHECK(cudaFreeAsync(p, c->stream));
+  q->arenas.clear();
+  q->arena_used = kArena;
+  q->nodes.clear();
+  q->versions.clear();
+  q->usage.clear();
+  q->max_level = 0;
+  q->replaying = false;
+  c->hw_pending = false;
+}
+
+void hw_release(Context* c) {
+  if (c->hw_queue == nullptr) return;
+  hw_replay(c);
+  delete c->hw_queue;
+  c->hw_queue = nullptr;
+}
+
+// Records res = a (kind) b.  Returns false when recording is switched off
+// (FHERT_EAGER_HW=1) and the caller has to launch the operation itself.
+bool hw_record(Context* c, HwKind kind, int64_t* res, const int64_t* a, const int64_t* b,
+               const uint32_t* table, int64_t scalar, int prime) {
+  HwQueue* q = queue_of(c);
+  if (q->eager) return false;
+  u64* dst   = reinterpret_cast<u64*>(res);
+  u64* src[3] = {reinterpret_cast<u64*>(const_cast<int64_t*>(a)),
+                 kind <= HW_MULADD ? reinterpret_cast<u64*>(const_cast<int64_t*>(b)) : nullptr,
+                 kind == HW_MULADD ? dst : nullptr};
+  Node nd{};
+  nd.kind        = kind;
+  nd.item.table  = table;
+  nd.item.scalar = scalar;
+  nd.item.prime  = (uint32_t)prime;
+  nd.dead        = false;
+  int  level     = 0;
+  bool in_place  = false;
+  const u64* phys[3] = {nullptr, nullptr, nullptr};
+  for (int i = 0; i < 3; i++) {
+    if (src[i] == nullptr) continue;
+    Version& v = version_of(q, src[i]);
+    phys[i]    = v.phys;
+    level      = std::max(level, v.writer_level);
+    if (src[i] == dst) in_place = true;
+  }
+  level += 1;
+  Version& dv = version_of(q, dst);
+  u64*     out;
+  if (!in_place && dv.readers > 0) {
+    out = scratch_limb(c, q);  // earlier readers keep the old value
+  } else {
+    out = dv.phys;
+    if (!in_place && dv.readers == 0 && dv.writer >= 0) q->nodes[dv.writer].dead = true;
+    Usage& u = q->usage[out];
+    level    = std::max(level, std::max(u.read_level, u.write_level) + 1);
+  }
+  for (int i = 0; i < 3; i++) {
+    if (src[i] == nullptr) continue;
+    Version& v = version_of(q, src[i]);
+    v.readers++;
+    Usage& u     = q->usage[v.phys];
+    u.read_level = std::max(u.read_level, level);
+  }
+  nd.item.dst = out;
+  nd.item.a   = phys[0];
+  nd.item.b   = phys[1];
+  nd.level    = level;
+  q->usage[out].write_level = level;
+  Version& fresh    = version_of(q, dst);
+  fresh.phys        = out;
+  fresh.writer      = (int)q->nodes.size();
+  fresh.writer_level = level;
+  fresh.readers     = 0;
+  q->nodes.push_back(nd);
+  q->max_level  = std::max(q->max_level, level);
+  c->hw_pending = true;
+  if ((int)q->nodes.size() >= kMaxNodes) hw_replay(c);
+  return true;
+}
+
+}  // namespace fhert

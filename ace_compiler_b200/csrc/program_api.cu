@@ -2,6 +2,8 @@
 // ciphertext metadata initialisers, accessors, tensors, program input/output
 // and the per-operator timer.  Semantics follow the CPU runtime function of
 // the same name; citations name files inside fhe-cmplr/rtlib/.
+#include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <ctime>
 #include <map>
@@ -256,6 +258,39 @@ void Print_tensor(FILE* fp, TENSOR* t) {
   }
   std::fprintf(fp, "\n]\n");
   std::fflush(stdout);
+}
+
+// ---- result checks a program compiled with run-time validation calls
+// (common/src/rt_validate.c:16-57)
+void Validate_impl(double* res, double* msg, uint32_t len, int32_t epsilon) {
+  double   error = std::pow(10, epsilon);
+  uint32_t bad   = len;
+  for (uint32_t i = 0; i < len; i++)
+    if (std::fabs(res[i] - msg[i]) > error) {
+      bad = i;
+      break;
+    }
+  if (bad < len) {
+    std::fprintf(stderr, "ERROR: validation failed at %d. %f != %f\n", bad, res[bad], msg[bad]);
+    uint32_t start = bad > 4 ? bad - 4 : 0, end = std::min(start + 8, len);
+    for (const char* row : {"idx", "res", "std"}) {
+      std::fprintf(stderr, "%s: ", row);
+      for (uint32_t j = start; j < end; j++) {
+        if (row[0] == 'i') std::fprintf(stderr, "%7d%c ", j, j == bad ? '*' : ' ');
+        else std::fprintf(stderr, "%8.4f ", row[0] == 'r' ? res[j] : msg[j]);
+      }
+      std::fprintf(stderr, "\n");
+    }
+  }
+  std::fprintf(stdout, "%s: internal validation %s.\n", bad < len ? "ERROR" : "INFO",
+               bad < len ? "fail" : "pass");
+  std::fflush(stdout);
+}
+
+void Validate_value_range(bool within_range) {
+  if (!within_range)
+    std::fprintf(stdout,
+                 "Please set a higher level or increase the difference between q0 and sf.\n");
 }
 
 // ---- timer (common/src/rt_stat.c:23-31); scripts parse this line format

@@ -134,6 +134,10 @@ struct Context {
   std::vector<uint32_t> fft_rot_group;
   // bootstrapping precomputation per slot count, owned by bootstrap.cu
   void* bootstrap = nullptr;
+  // recorded per-limb vector operations awaiting replay (hw_queue.cu)
+  struct HwQueue* hw_queue   = nullptr;
+  bool            hw_pending = false;
+  uint64_t        hw_batched_limbs = 0;
 
   cudaStream_t stream = nullptr;
   uint64_t     launches = 0;
@@ -155,7 +159,8 @@ extern const char* const kKernelNames[KID_COUNT];
 void prof_before(KernelId id);
 void prof_after(KernelId id, int limbs);  // limbs = limbs the launch covered
 
-Context* ctx();               // aborts when no context exists
+Context* ctx();               // aborts when no context exists; replays recorded Hw_* calls
+Context* ctx_noflush();       // same without the replay (accessors, the Hw_* calls themselves)
 Context* ctx_or_null();
 int64_t* scratch(size_t words);  // stream-ordered scratch, grows on demand
 void     prof_begin();
@@ -203,6 +208,16 @@ void encode_vector(Context* c, PLAIN plain, std::vector<std::complex<double>>& v
 // special limbs
 std::vector<int64_t> encode_value(Context* c, double value, uint32_t level, double scale,
                                   uint32_t num_p);
+
+// ---- hw_queue.cu: deferred per-limb vector operations ----
+enum HwKind : uint8_t {
+  HW_ADD, HW_SUB, HW_MUL, HW_MULADD, HW_ADD_SCALAR, HW_MUL_SCALAR, HW_ROTATE, HW_COPY
+};
+// records res = a (kind) b on one limb; false = recording is off, launch now
+bool hw_record(Context* c, HwKind kind, int64_t* res, const int64_t* a, const int64_t* b,
+               const uint32_t* table, int64_t scalar, int prime);
+void hw_replay(Context* c);   // run everything recorded so far
+void hw_release(Context* c);
 
 // ---- bootstrap.cu ----
 // builds the linear-transform plaintexts and the rotation / conjugation keys

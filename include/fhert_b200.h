@@ -29,6 +29,7 @@
 #include <stddef.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #ifdef __cplusplus
 extern "C" {
@@ -429,6 +430,18 @@ void* Pt_from_msg_ofst(void* pt, uint32_t index, size_t ofst, size_t len, uint32
                        uint32_t level);
 void  Free_data(void* poly);
 void  Fhert_pt_cache_stats(size_t* entries, size_t* bytes, size_t* hits, size_t* misses);
+
+/* Checks emitted by the compiler's run-time validation mode
+ * (include/common/rt_validate.h:20-49, common/src/rt_validate.c:16-57) */
+void Validate_impl(double* res, double* msg, uint32_t len, int32_t epsilon);
+void Validate_value_range(bool within_range);
+bool Within_value_range(CIPHER ciph, double* msg, uint32_t len); /* cipher.c:172 */
+static inline void Validate(CIPHER ciph, double* msg, uint32_t len, int32_t epsilon) {
+  double* res = Get_msg(ciph);
+  Validate_impl(res, msg, len, epsilon);
+  free(res);
+  Validate_value_range(Within_value_range(ciph, msg, len));
+}
 
 /* per-operator timer; prints "[RT_STAT] <msg> takes <s> seconds." after
  * draining the stream, so queued kernels are charged to their operator */

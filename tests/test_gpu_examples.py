@@ -26,7 +26,7 @@ NAMES = sorted(f for f in (os.listdir(EXAMPLES) if os.path.isdir(EXAMPLES) else 
 
 @pytest.mark.gpu
 def test_examples_were_built():
-    assert len(NAMES) >= 11, f"expected the example programs under {EXAMPLES}, found {NAMES}"
+    assert len(NAMES) >= 15, f"expected the example programs under {EXAMPLES}, found {NAMES}"
 
 
 @pytest.mark.gpu
@@ -36,5 +36,11 @@ def test_example_program(name):
     run = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     tail = (run.stdout + run.stderr)[-2000:]
     assert run.returncode == 0, tail
+    if name == "eg_fhertlib_mul_const_rtv":
+        # this one feeds a message that is too large for its modulus and expects
+        # the run-time validation to notice
+        assert "EXPECTED FAILED!" in run.stdout, tail
+        assert "internal validation fail" in run.stdout, tail
+        return
     assert "SUCESS!" in run.stdout, tail
     assert "FAILED" not in run.stdout, tail

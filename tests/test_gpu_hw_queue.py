@@ -1,0 +1,129 @@
+"""Deferred per-limb operations: random sequences of Hw_* calls, including
+in-place updates, a shared scratch limb reused by every step, dead stores and
+limb copies, must leave exactly what running them one by one would."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+N, L = 1024, 4
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    import ace_compiler_b200 as rt
+    g = rt.Runtime(N, L, 60, 56, 2, rot_idxs=(1, 3))
+    yield g
+    g.close()
+
+
+def run_program(gpu, seed, steps, limbs=10):
+    lib = gpu.lib
+    rng = np.random.default_rng(seed)
+    primes = gpu.primes
+    # every limb buffer belongs to one prime; operations stay within a prime
+    owner = [int(rng.integers(0, 2)) for _ in range(limbs)]
+    poly = gpu.new_poly(limbs)
+    host = np.stack([rng.integers(0, primes[owner[i]], N, dtype=np.int64) for i in range(limbs)])
+    gpu.upload(poly, host)
+    model = [host[i].astype(object) for i in range(limbs)]
+    order_dev = lib.Auto_order(1)
+    # the permutation itself: rotate the identity vector once
+    ident = gpu.new_poly(2)
+    gpu.upload(ident, np.stack([np.arange(N, dtype=np.int64), np.zeros(N, np.int64)]))
+    lib.Hw_rotate(gpu.limb_ptr(ident, 1), gpu.limb_ptr(ident, 0), order_dev, gpu.modulus(0), N)
+    table = gpu.download(ident)[1].astype(np.int64)
+    gpu.free(ident)
+
+    def ptr(i):
+        return gpu.limb_ptr(poly, i)
+
+    def mod(i):
+        return gpu.modulus(owner[i])
+
+    for step in range(steps):
+        kind = int(rng.integers(0, 9))
+        d = int(rng.integers(0, limbs))
+        same = [i for i in range(limbs) if owner[i] == owner[d]]
+        a = int(rng.choice(same))
+        b = int(rng.choice(same))
+        q = primes[owner[d]]
+        if step % 5 == 0:
+            d = 0 if owner[0] == owner[d] else d  # limb 0 doubles as the shared scratch
+            same = [i for i in range(limbs) if owner[i] == owner[d]]
+            a, b = int(rng.choice(same)), int(rng.choice(same))
+        if kind == 0:
+            lib.Hw_modadd(ptr(d), ptr(a), ptr(b), mod(d), N)
+            model[d] = (model[a] + model[b]) % q
+        elif kind == 1:
+            lib.Hw_modsub(ptr(d), ptr(a), ptr(b), mod(d), N)
+            model[d] = (model[a] - model[b]) % q
+        elif kind == 2:
+            lib.Hw_modmul(ptr(d), ptr(a), ptr(b), mod(d), N)
+            model[d] = (model[a] * model[b]) % q
+        elif kind == 3:
+            lib.Hw_modmuladd(ptr(d), ptr(a), ptr(b), mod(d), N)
+            model[d] = (model[d] + model[a] * model[b]) % q
+        elif kind == 4:
+            s = int(rng.integers(-2 ** 40, 2 ** 40))
+            lib.Hw_modadd_scalar(ptr(d), ptr(a), s, mod(d), N)
+            model[d] = (model[a] + s) % q
+        elif kind == 5:
+            s = int(rng.integers(-2 ** 40, 2 ** 40))
+            lib.Hw_modmul_scalar(ptr(d), ptr(a), s, mod(d), N)
+            model[d] = (model[a] * s) % q
+        elif kind == 6:
+            if a == d:
+                continue
+            lib.Hw_rotate(ptr(d), ptr(a), order_dev, mod(d), N)
+            model[d] = model[a][table]
+        elif kind == 7:
+            lib.Set_coeffs(poly, d, N, ptr(a))
+            model[d] = model[a].copy()
+        else:
+            if step % 3 == 0:
+                lib.Fhert_sync()  # an unrelated entry point in the middle of a sequence
+    got = gpu.download(poly)
+    want = np.stack([m.astype(np.int64) for m in model])
+    gpu.free(poly)
+    return got, want
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_limb_programs(gpu, seed):
+    before = gpu.lib.Fhert_kernel_launches()
+    got, want = run_program(gpu, seed, 400)
+    assert np.array_equal(got, want)
+    launches = gpu.lib.Fhert_kernel_launches() - before
+    assert launches < 400  # recorded calls were merged into fewer launches
+
+
+def test_key_switch_idiom_is_merged(gpu):
+    """tmp = key * digit; acc += tmp for every limb with one shared tmp: two
+    launches, not two per limb."""
+    lib = gpu.lib
+    rng = np.random.default_rng(11)
+    limbs = 32
+    q = gpu.primes[0]
+    key = gpu.new_poly(limbs); dig = gpu.new_poly(limbs); acc = gpu.new_poly(limbs)
+    tmp = gpu.new_poly(1)
+    hk = rng.integers(0, q, (limbs, N), dtype=np.int64)
+    hd = rng.integers(0, q, (limbs, N), dtype=np.int64)
+    ha = rng.integers(0, q, (limbs, N), dtype=np.int64)
+    gpu.upload(key, hk); gpu.upload(dig, hd); gpu.upload(acc, ha)
+    m0 = gpu.modulus(0)
+    lib.Fhert_sync()
+    before = lib.Fhert_kernel_launches()
+    for i in range(limbs):
+        lib.Hw_modmul(lib.Coeffs(tmp, 0, N), lib.Coeffs(key, i, N), lib.Coeffs(dig, i, N), m0, N)
+        lib.Hw_modadd(lib.Coeffs(acc, i, N), lib.Coeffs(acc, i, N), lib.Coeffs(tmp, 0, N), m0, N)
+    lib.Fhert_sync()
+    assert lib.Fhert_kernel_launches() - before <= 3
+    want = (ha.astype(object) + hk.astype(object) * hd.astype(object)) % q
+    assert np.array_equal(gpu.download(acc), want.astype(np.int64))
+    last = (hk[-1].astype(object) * hd[-1].astype(object)) % q
+    assert np.array_equal(gpu.download(tmp)[0], last.astype(np.int64))
+    for p in (key, dig, acc, tmp):
+        gpu.free(p)
