@@ -131,8 +131,12 @@ void Prepare_context(void) {
   // ckks_context.c:151-154: open the program's weight file when it names one
   RT_DATA_INFO* info = Get_rt_data_info();
   if (info != nullptr) {
-    bool ok = Pt_mgr_init(info->_file_name);
-    FHERT_ASSERT(ok, "cannot open data file %s", info->_file_name);
+    // FHERT_DATA_FILE points a program at a weight file somewhere else than
+    // the path compiled into it
+    const char* moved = std::getenv("FHERT_DATA_FILE");
+    const char* path  = moved != nullptr && moved[0] != '\0' ? moved : info->_file_name;
+    bool        ok    = Pt_mgr_init(path);
+    FHERT_ASSERT(ok, "cannot open data file %s", path);
   }
   std::printf(
       "ckks_param: _provider = %d, _poly_degree = %d, mul_depth = %ld, input_lev = %ld, "
@@ -195,7 +199,8 @@ void Alloc_poly_data(POLY poly, uint32_t degree, size_t num_q, size_t num_p) {
 void Free_poly_data(POLY poly) {
   // rns_poly.c:1319-1325
   if (poly->_data) {
-    CUDA_CHECK(cudaFreeAsync(poly->_data, ctx()->stream));
+    Context* c = ctx();
+    if (!pt_cache_owns(poly->_data)) CUDA_CHECK(cudaFreeAsync(poly->_data, c->stream));
     poly->_data = nullptr;
   }
   poly->_num_alloc_primes = 0;

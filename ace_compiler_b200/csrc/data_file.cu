@@ -112,6 +112,12 @@ void* plain_from_entry(void* pt, uint32_t index, size_t ofst, size_t len, uint32
 
 }  // namespace
 
+namespace fhert {
+// programs of the older generation release plaintexts with Free_poly_data;
+// limbs lent out by the cache must survive that
+bool pt_cache_owns(const void* data) { return g_cache.budget != 0 && cache_owns(data); }
+}  // namespace fhert
+
 extern "C" {
 
 bool Pt_mgr_init(const char* fname) {

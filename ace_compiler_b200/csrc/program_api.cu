@@ -108,7 +108,13 @@ IoTable g_io;
 
 CIPHERTEXT* new_ciph() { return (CIPHERTEXT*)std::calloc(1, sizeof(CIPHERTEXT)); }
 
-clock_t g_tm_stamp = 0;
+double g_tm_stamp = 0;
+
+double wall_seconds() {
+  struct timespec ts;
+  clock_gettime(CLOCK_MONOTONIC, &ts);
+  return (double)ts.tv_sec + 1e-9 * (double)ts.tv_nsec;
+}
 
 }  // namespace
 
@@ -294,13 +300,27 @@ void Validate_value_range(bool within_range) {
 }
 
 // ---- timer (common/src/rt_stat.c:23-31); scripts parse this line format
-void Tm_start(const char*) { g_tm_stamp = clock(); }
+// FHERT_RT_STAT=0 silences the lines and skips the device drain they need
+static bool tm_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = std::getenv("FHERT_RT_STAT");
+    on            = !(e != nullptr && e[0] == '0');
+  }
+  return on != 0;
+}
+
+void Tm_start(const char*) {
+  if (!tm_enabled()) return;
+  Fhert_sync();
+  g_tm_stamp = wall_seconds();
+}
 
 void Tm_taken(const char* msg) {
+  if (!tm_enabled()) return;
   Fhert_sync();  // the queued kernels belong to the operator being timed
-  clock_t now = clock();
-  std::fprintf(stdout, "[RT_STAT] %s takes %.3f seconds.\n", msg,
-               ((double)(now - g_tm_stamp)) / (double)CLOCKS_PER_SEC);
+  double now = wall_seconds();
+  std::fprintf(stdout, "[RT_STAT] %s takes %.3f seconds.\n", msg, now - g_tm_stamp);
   g_tm_stamp = now;
   std::fflush(stdout);
 }

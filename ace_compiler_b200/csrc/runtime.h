@@ -219,6 +219,9 @@ bool hw_record(Context* c, HwKind kind, int64_t* res, const int64_t* a, const in
 void hw_replay(Context* c);   // run everything recorded so far
 void hw_release(Context* c);
 
+// ---- data_file.cu ----
+bool pt_cache_owns(const void* data);  // limb storage lent out by the plaintext cache
+
 // ---- bootstrap.cu ----
 // builds the linear-transform plaintexts and the rotation / conjugation keys
 // for `slots` (0 = N/2) when the context is deep enough (ckks_context.c:239-262)

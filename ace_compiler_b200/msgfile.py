@@ -39,3 +39,29 @@ def write_msg_file(path, entries, model=b"synthetic", uuid=b"0" * 36):
         f.write(payload)
         f.write(lut)
     return lut_ofst
+
+
+def write_synthetic_msg_file(path, entry_count, entry_floats=32768, distinct=64, sigma=0.05, seed=7):
+    """A stand-in for a compiled model's weight file: entry_count entries of
+    entry_floats seeded N(0, sigma) floats each.  Only `distinct` different
+    payload rows are stored; the lookup table points every entry at one of
+    them, which keeps the file small while each entry keeps its own index
+    (and so its own slot in the plaintext cache)."""
+    rng = np.random.default_rng(seed)
+    rows = rng.normal(0.0, sigma, (distinct, entry_floats)).astype(np.float32)
+    payload = rows.tobytes()
+    row_bytes = entry_floats * 4
+    assert row_bytes % (1 << ALIGN_LOG2) == 0
+    lut = bytearray()
+    for index in range(entry_count):
+        offset = PAGE + (index % distinct) * row_bytes
+        packed = 1 | (0 << 8) | (offset << 16)
+        lut += struct.pack("<16sIIQ", b"w%d" % index, index, row_bytes, packed)
+    lut_ofst = PAGE + len(payload)
+    header = struct.pack("<8sIHBBQQqq48s40s", b"!ANTFHE\0", 0, 0, DE_MSG_F32, ALIGN_LOG2,
+                         entry_count, lut_ofst, 0, 0, b"synthetic", b"0" * 36)
+    with open(path, "wb") as f:
+        f.write(header + b"\0" * (PAGE - len(header)))
+        f.write(payload)
+        f.write(lut)
+    return lut_ofst

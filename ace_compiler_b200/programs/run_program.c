@@ -1,0 +1,83 @@
+/* Driver for a program emitted by the ANT-ACE compiler, linked against the
+ * B200 runtime.  It plays the part of the hand-written main() that the
+ * compiler's users put around a generated file: build the context the program
+ * asks for, encrypt one synthetic input tensor per image, run the program's
+ * Main_graph, decrypt.  Inputs are seeded uniform[-1, 1) values; timings are
+ * wall-clock around each stage with the device drained.
+ *
+ * usage: run_program [--shape n,c,h,w] [--seed s] [--images k] [--input name]
+ *                    [--output name] [--values m]
+ * prints one JSON line per image:
+ *   {"image": i, "encrypt_s": .., "infer_s": .., "decrypt_s": .., "logits": [..]}
+ * and a final line {"setup_s": .., "images": k, "mean_infer_s": ..}.
+ * FHERT_DATA_FILE=<path> replaces the weight file path compiled into the
+ * program. */
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <time.h>
+
+#include "common/rtlib.h"
+
+static double now_s(void) {
+  struct timespec ts;
+  clock_gettime(CLOCK_MONOTONIC, &ts);
+  return (double)ts.tv_sec + 1e-9 * (double)ts.tv_nsec;
+}
+
+/* splitmix64: the same stream on every machine */
+static uint64_t next_u64(uint64_t* s) {
+  uint64_t z = (*s += 0x9E3779B97F4A7C15ull);
+  z          = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z          = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+int main(int argc, char** argv) {
+  size_t      shape[4] = {1, 3, 32, 32};
+  uint64_t    seed     = 1;
+  int         images = 1, values = 10;
+  const char *in_name = "input", *out_name = "output";
+  for (int i = 1; i + 1 < argc; i += 2) {
+    if (!strcmp(argv[i], "--shape"))
+      sscanf(argv[i + 1], "%zu,%zu,%zu,%zu", &shape[0], &shape[1], &shape[2], &shape[3]);
+    else if (!strcmp(argv[i], "--seed")) seed = strtoull(argv[i + 1], NULL, 10);
+    else if (!strcmp(argv[i], "--images")) images = atoi(argv[i + 1]);
+    else if (!strcmp(argv[i], "--values")) values = atoi(argv[i + 1]);
+    else if (!strcmp(argv[i], "--input")) in_name = argv[i + 1];
+    else if (!strcmp(argv[i], "--output")) out_name = argv[i + 1];
+  }
+  double t0 = now_s();
+  Prepare_context();
+  Fhert_sync();
+  double setup = now_s() - t0, total = 0;
+  size_t count = shape[0] * shape[1] * shape[2] * shape[3];
+  for (int img = 0; img < images; img++) {
+    TENSOR* t = Alloc_tensor(shape[0], shape[1], shape[2], shape[3], NULL);
+    for (size_t k = 0; k < count; k++)
+      t->_vals[k] = (double)(next_u64(&seed) >> 11) / 4503599627370496.0 - 1.0;
+    double a = now_s();
+    Prepare_input(t, in_name);
+    Fhert_sync();
+    double b = now_s();
+    Free_tensor(t);
+    Run_main_graph();
+    Fhert_sync();
+    double c = now_s();
+    double* out = Handle_output(out_name);
+    double  d   = now_s();
+    printf("{\"image\": %d, \"encrypt_s\": %.6f, \"infer_s\": %.6f, \"decrypt_s\": %.6f, "
+           "\"launches\": %llu, \"logits\": [",
+           img, b - a, c - b, d - c, (unsigned long long)Fhert_kernel_launches());
+    for (int k = 0; k < values; k++) printf("%s%.6f", k ? ", " : "", out[k]);
+    printf("]}\n");
+    fflush(stdout);
+    free(out);
+    total += c - b;
+  }
+  printf("{\"setup_s\": %.3f, \"images\": %d, \"mean_infer_s\": %.6f}\n", setup, images,
+         total / (images > 0 ? images : 1));
+  Finalize_context();
+  return 0;
+}
