@@ -103,6 +103,7 @@ SIGNATURES = {
     "Fhert_download": (None, [POLY, C.c_size_t, C.c_size_t, C.c_void_p]),
     "Fhert_sync": (None, []),
     "Fhert_stream": (C.c_void_p, []),
+    "Fhert_transfer_bytes": (None, [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "Fhert_kernel_launches": (C.c_uint64, []),
     "Fhert_profile_begin": (None, []),
     "Fhert_profile_end": (C.c_size_t, [C.c_char_p, C.c_size_t]),

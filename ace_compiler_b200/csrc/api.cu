@@ -242,10 +242,10 @@ void Copy_poly(POLY res, POLY poly) {
   FHERT_ASSERT(res->_num_primes == poly->_num_primes && res->_num_primes_p >= poly->_num_primes_p,
                "Copy_poly: size not match");
   size_t n = poly->_ring_degree;
-  CUDA_CHECK(cudaMemcpyAsync(res->_data, poly->_data, poly->_num_primes * n * sizeof(int64_t),
+  CUDA_CHECK(counted_copy(res->_data, poly->_data, poly->_num_primes * n * sizeof(int64_t),
                              cudaMemcpyDeviceToDevice, c->stream));
   if (poly->_num_primes_p)
-    CUDA_CHECK(cudaMemcpyAsync(res->_data + p_offset(res) * n, poly->_data + p_offset(poly) * n,
+    CUDA_CHECK(counted_copy(res->_data + p_offset(res) * n, poly->_data + p_offset(poly) * n,
                                res->_num_primes_p * n * sizeof(int64_t),
                                cudaMemcpyDeviceToDevice, c->stream));
   res->_is_ntt = poly->_is_ntt;
@@ -260,14 +260,14 @@ void Set_coeffs(POLY poly, uint32_t limb, uint32_t degree, int64_t* src) {
   if (dst == src) return;
   Context* c = ctx_noflush();
   if (degree == c->N && hw_record(c, HW_COPY, dst, src, nullptr, nullptr, 0, 0)) return;
-  CUDA_CHECK(cudaMemcpyAsync(dst, src, (size_t)degree * sizeof(int64_t),
+  CUDA_CHECK(counted_copy(dst, src, (size_t)degree * sizeof(int64_t),
                              cudaMemcpyDeviceToDevice, ctx()->stream));
 }
 
 void Fhert_upload(POLY poly, size_t first, size_t limbs, const int64_t* host) {
   FHERT_ASSERT(poly->_data && first + limbs <= poly->_num_alloc_primes, "upload out of range");
   size_t n = poly->_ring_degree;
-  CUDA_CHECK(cudaMemcpyAsync(poly->_data + first * n, host, limbs * n * sizeof(int64_t),
+  CUDA_CHECK(counted_copy(poly->_data + first * n, host, limbs * n * sizeof(int64_t),
                              cudaMemcpyHostToDevice, ctx()->stream));
 }
 
@@ -275,7 +275,7 @@ void Fhert_download(POLY poly, size_t first, size_t limbs, int64_t* host) {
   FHERT_ASSERT(poly->_data && first + limbs <= poly->_num_alloc_primes,
                "download out of range");
   size_t n = poly->_ring_degree;
-  CUDA_CHECK(cudaMemcpyAsync(host, poly->_data + first * n, limbs * n * sizeof(int64_t),
+  CUDA_CHECK(counted_copy(host, poly->_data + first * n, limbs * n * sizeof(int64_t),
                              cudaMemcpyDeviceToHost, ctx()->stream));
   CUDA_CHECK(cudaStreamSynchronize(ctx()->stream));
 }
@@ -283,6 +283,11 @@ void Fhert_download(POLY poly, size_t first, size_t limbs, int64_t* host) {
 void     Fhert_sync(void) { CUDA_CHECK(cudaStreamSynchronize(ctx()->stream)); }
 void*    Fhert_stream(void) { return (void*)ctx()->stream; }
 uint64_t Fhert_kernel_launches(void) { return ctx_or_null() ? ctx()->launches : 0; }
+void     Fhert_transfer_bytes(uint64_t* h2d, uint64_t* d2h) {
+  Context* c = ctx_or_null();
+  if (h2d) *h2d = c ? c->h2d_bytes : 0;
+  if (d2h) *d2h = c ? c->d2h_bytes : 0;
+}
 void     Fhert_profile_begin(void) { prof_begin(); }
 size_t   Fhert_profile_end(char* buf, size_t cap) { return prof_end(buf, cap); }
 
@@ -393,7 +398,7 @@ POLY Modswitch(POLY res, POLY poly) {
   FHERT_ASSERT(level >= 2, "polynomial level is too small to support modswitch");
   if (res != poly) {
     ensure_poly(res, poly->_ring_degree, level - 1, poly->_num_primes_p);
-    CUDA_CHECK(cudaMemcpyAsync(res->_data, poly->_data,
+    CUDA_CHECK(counted_copy(res->_data, poly->_data,
                                (level - 1) * poly->_ring_degree * sizeof(int64_t),
                                cudaMemcpyDeviceToDevice, ctx()->stream));
     res->_is_ntt = poly->_is_ntt;
@@ -470,7 +475,7 @@ POLY Decomp(POLY res, POLY poly, uint32_t part) {
     res->_num_primes   = len;
     res->_num_primes_p = 0;
   }
-  CUDA_CHECK(cudaMemcpyAsync(res->_data, poly->_data + start * c->N,
+  CUDA_CHECK(counted_copy(res->_data, poly->_data + start * c->N,
                              len * c->N * sizeof(int64_t), cudaMemcpyDeviceToDevice, c->stream));
   res->_is_ntt = poly->_is_ntt;
   return res;
@@ -555,7 +560,7 @@ POLY Decomp_modup(POLY res, POLY poly, uint32_t part) {
   size_t len = std::min((size_t)c->alpha, level - start);
   fhert_raise_parts(c, poly->_data, poly->_is_ntt, level, (int)part, (int)part + 1, res->_data, 0,
               (int)p_offset(res));
-  CUDA_CHECK(cudaMemcpyAsync(res->_data + start * c->N, poly->_data + start * c->N,
+  CUDA_CHECK(counted_copy(res->_data + start * c->N, poly->_data + start * c->N,
                              len * c->N * sizeof(int64_t), cudaMemcpyDeviceToDevice, c->stream));
   res->_is_ntt = poly->_is_ntt;
   return res;
@@ -569,7 +574,7 @@ POLY Mod_up(POLY res, POLY old_poly, uint32_t part) {
   size_t start = (size_t)c->alpha * part;
   size_t len   = old_poly->_num_primes;
   // place the digit at its own limbs of res, then raise from there
-  CUDA_CHECK(cudaMemcpyAsync(res->_data + start * c->N, old_poly->_data,
+  CUDA_CHECK(counted_copy(res->_data + start * c->N, old_poly->_data,
                              len * c->N * sizeof(int64_t), cudaMemcpyDeviceToDevice, c->stream));
   fhert_raise_parts(c, res->_data, old_poly->_is_ntt, level, (int)part, (int)part + 1, res->_data, 0,
               (int)p_offset(res));
@@ -752,7 +757,7 @@ void Fhert_import_switch_key(bool is_rot, int32_t rot_idx, uint32_t part, int wh
   FHERT_ASSERT(part < k->_num_parts, "digit out of range");
   POLY   p     = which == 0 ? &k->_parts[part]._p0 : &k->_parts[part]._p1;
   size_t bytes = (size_t)(c->L + c->K) * c->N * sizeof(int64_t);
-  CUDA_CHECK(cudaMemcpyAsync(p->_data, host, bytes, cudaMemcpyHostToDevice, c->stream));
+  CUDA_CHECK(counted_copy(p->_data, host, bytes, cudaMemcpyHostToDevice, c->stream));
   CUDA_CHECK(cudaStreamSynchronize(c->stream));
 }
 

@@ -528,7 +528,7 @@ void mul_monomial(Context* c, CIPHER res, CIPHER a, uint32_t power) {
   std::vector<int64_t> one(level);
   for (size_t i = 0; i < level; i++) one[i] = reduced < n ? 1 : (int64_t)c->primes[i] - 1;
   for (size_t i = 0; i < level; i++)
-    CUDA_CHECK(cudaMemcpyAsync(mono._data + i * n + index, &one[i], sizeof(int64_t),
+    CUDA_CHECK(counted_copy(mono._data + i * n + index, &one[i], sizeof(int64_t),
                                cudaMemcpyHostToDevice, c->stream));
   CUDA_CHECK(cudaStreamSynchronize(c->stream));
   Conv_poly2ntt_inplace(&mono);
@@ -926,7 +926,7 @@ void rotate_stage(Context* c, CIPHER ct, std::vector<PLAINTEXT>& plains, const F
     int64_t* dst = rot.p + (size_t)j * 2 * pw;
     int32_t  val = rot_in[j];
     if (val == 0) {
-      CUDA_CHECK(cudaMemcpyAsync(dst, lifted.p, 2 * pw * sizeof(int64_t), cudaMemcpyDeviceToDevice,
+      CUDA_CHECK(counted_copy(dst, lifted.p, 2 * pw * sizeof(int64_t), cudaMemcpyDeviceToDevice,
                                  c->stream));
       continue;
     }
@@ -968,10 +968,10 @@ void rotate_stage(Context* c, CIPHER ct, std::vector<PLAINTEXT>& plains, const F
     launch_inner_product(args);
 
     if (i == 0) {
-      CUDA_CHECK(cudaMemcpyAsync(first.p, inner.p, pw * sizeof(int64_t), cudaMemcpyDeviceToDevice,
+      CUDA_CHECK(counted_copy(first.p, inner.p, pw * sizeof(int64_t), cudaMemcpyDeviceToDevice,
                                  c->stream));
       CUDA_CHECK(cudaMemsetAsync(outer.p, 0, pw * sizeof(int64_t), c->stream));
-      CUDA_CHECK(cudaMemcpyAsync(outer.p + pw, inner.p + pw, pw * sizeof(int64_t),
+      CUDA_CHECK(counted_copy(outer.p + pw, inner.p + pw, pw * sizeof(int64_t),
                                  cudaMemcpyDeviceToDevice, c->stream));
       continue;
     }

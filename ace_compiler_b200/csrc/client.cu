@@ -123,7 +123,7 @@ LimbBatch dense_batch(Context* c, size_t level, size_t num_p) {
 int64_t* upload_samples(Context* c, const std::vector<int64_t>& v) {
   int64_t* d = nullptr;
   CUDA_CHECK(cudaMallocAsync(&d, v.size() * sizeof(int64_t), c->stream));
-  CUDA_CHECK(cudaMemcpyAsync(d, v.data(), v.size() * sizeof(int64_t), cudaMemcpyHostToDevice,
+  CUDA_CHECK(counted_copy(d, v.data(), v.size() * sizeof(int64_t), cudaMemcpyHostToDevice,
                              c->stream));
   // the host vector may go out of scope before the copy is consumed
   CUDA_CHECK(cudaStreamSynchronize(c->stream));
@@ -150,7 +150,7 @@ void sample_uniform_poly(Context* c, POLY a) {
     sample_uniform(host.data() + i * c->N, c->N, c->primes[i]);
   for (size_t k = 0; k < a->_num_primes_p; k++)
     sample_uniform(host.data() + (a->_num_primes + k) * c->N, c->N, c->primes[c->L + k]);
-  CUDA_CHECK(cudaMemcpyAsync(a->_data, host.data(), host.size() * sizeof(int64_t),
+  CUDA_CHECK(counted_copy(a->_data, host.data(), host.size() * sizeof(int64_t),
                              cudaMemcpyHostToDevice, c->stream));
   CUDA_CHECK(cudaStreamSynchronize(c->stream));
 }
@@ -238,7 +238,7 @@ void generate_keys(Context* c) {
   }
   Alloc_poly_data(&c->sk_s, n, L, K);
   Alloc_poly_data(&c->sk_ntt, n, L, K);
-  CUDA_CHECK(cudaMemcpyAsync(c->sk_s._data, host.data(), host.size() * sizeof(int64_t),
+  CUDA_CHECK(counted_copy(c->sk_s._data, host.data(), host.size() * sizeof(int64_t),
                              cudaMemcpyHostToDevice, c->stream));
   CUDA_CHECK(cudaStreamSynchronize(c->stream));
   Copy_poly(&c->sk_ntt, &c->sk_s);

@@ -193,7 +193,7 @@ void encode_vector(Context* c, PLAIN plain, std::vector<cplx>& values, uint32_t 
   int64_t* d_msg = nullptr;
   u64*     d_pow = nullptr;
   CUDA_CHECK(cudaMallocAsync(&d_msg, n * sizeof(int64_t), c->stream));
-  CUDA_CHECK(cudaMemcpyAsync(d_msg, msg.data(), n * sizeof(int64_t), cudaMemcpyHostToDevice,
+  CUDA_CHECK(counted_copy(d_msg, msg.data(), n * sizeof(int64_t), cudaMemcpyHostToDevice,
                              c->stream));
   std::vector<u64> powp;
   if (sf_degree > 1) {
@@ -205,7 +205,7 @@ void encode_vector(Context* c, PLAIN plain, std::vector<cplx>& values, uint32_t 
       powp[i] = p;
     }
     CUDA_CHECK(cudaMallocAsync(&d_pow, powp.size() * sizeof(u64), c->stream));
-    CUDA_CHECK(cudaMemcpyAsync(d_pow, powp.data(), powp.size() * sizeof(u64),
+    CUDA_CHECK(counted_copy(d_pow, powp.data(), powp.size() * sizeof(u64),
                                cudaMemcpyHostToDevice, c->stream));
   }
   launch_encode_split(plain->_poly._data, d_msg, d_pow, q_batch(level, num_p, c->L));
@@ -320,7 +320,7 @@ void error_poly(Context* c, POLY e, size_t level) {
   sample_triangle(tri.data(), c->N);
   int64_t* d = nullptr;
   CUDA_CHECK(cudaMallocAsync(&d, c->N * sizeof(int64_t), c->stream));
-  CUDA_CHECK(cudaMemcpyAsync(d, tri.data(), c->N * sizeof(int64_t), cudaMemcpyHostToDevice,
+  CUDA_CHECK(counted_copy(d, tri.data(), c->N * sizeof(int64_t), cudaMemcpyHostToDevice,
                              c->stream));
   Alloc_poly_data(e, c->N, level, 0);
   launch_small_to_rns(e->_data, d, q_batch(level));

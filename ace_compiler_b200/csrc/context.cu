@@ -551,7 +551,7 @@ void destroy_context() {
 const char* const kKernelNames[KID_COUNT] = {
     "ntt_strided", "ntt_contig", "ntt_small", "intt_strided", "intt_contig", "intt_small",
     "elementwise", "automorphism", "mul_const", "rescale_lift", "rescale_combine",
-    "base_conv", "moddown_combine", "inner_product", "mod_raise", "tensor"};
+    "base_conv", "moddown_combine", "inner_product", "mod_raise", "tensor", "hw_batch", "encode"};
 
 struct ProfState {
   bool                                    on = false;

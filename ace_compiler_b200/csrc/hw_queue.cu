@@ -136,6 +136,7 @@ void run_wave(Context* c, HwKind kind, const std::vector<const Node*>& wave) {
     l.count = (int)std::min<size_t>(kHwItems, wave.size() - off);
     for (int i = 0; i < l.count; i++) l.item[i] = wave[off + i]->item;
     dim3 grid((c->N + kThreads * 2 - 1) / (kThreads * 2), l.count);
+    prof_before(KID_HW_BATCH);
 #define HW_CASE(K)                                                                      \
   case K:                                                                               \
     hw_batch_kernel<K><<<grid, kThreads, 0, c->stream>>>(l, c->d_mod, c->N);            \
@@ -151,6 +152,7 @@ void run_wave(Context* c, HwKind kind, const std::vector<const Node*>& wave) {
       HW_CASE(HW_COPY)
     }
 #undef HW_CASE
+    prof_after(KID_HW_BATCH, l.count);
     c->launches++;
     c->hw_batched_limbs += l.count;
     CUDA_CHECK(cudaGetLastError());

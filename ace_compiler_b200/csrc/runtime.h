@@ -138,6 +138,8 @@ struct Context {
   struct HwQueue* hw_queue   = nullptr;
   bool            hw_pending = false;
   uint64_t        hw_batched_limbs = 0;
+  // bytes moved between host and device since the context was made
+  uint64_t h2d_bytes = 0, d2h_bytes = 0;
 
   cudaStream_t stream = nullptr;
   uint64_t     launches = 0;
@@ -152,7 +154,7 @@ enum KernelId {
   KID_NTT_STRIDED, KID_NTT_CONTIG, KID_NTT_SMALL, KID_INTT_STRIDED, KID_INTT_CONTIG,
   KID_INTT_SMALL, KID_ELEMENTWISE, KID_AUTOMORPHISM, KID_MUL_CONST, KID_RESCALE_LIFT,
   KID_RESCALE_COMBINE, KID_BASE_CONV, KID_MODDOWN_COMBINE, KID_INNER_PRODUCT, KID_MOD_RAISE,
-  KID_TENSOR,
+  KID_TENSOR, KID_HW_BATCH, KID_ENCODE,
   KID_COUNT
 };
 extern const char* const kKernelNames[KID_COUNT];
@@ -161,6 +163,10 @@ void prof_after(KernelId id, int limbs);  // limbs = limbs the launch covered
 
 Context* ctx();               // aborts when no context exists; replays recorded Hw_* calls
 Context* ctx_noflush();       // same without the replay (accessors, the Hw_* calls themselves)
+
+// cudaMemcpyAsync that also keeps the context's host<->device byte counters
+inline cudaError_t counted_copy(void* dst, const void* src, size_t bytes, cudaMemcpyKind kind,
+                                cudaStream_t stream);
 Context* ctx_or_null();
 int64_t* scratch(size_t words);  // stream-ordered scratch, grows on demand
 void     prof_begin();
@@ -315,6 +321,18 @@ void launch_inner_product(const InnerArgs& args);
 // Mod-raise (rns_poly.c:1101-1125): res[dst] = switch_modulus(src, q_0 -> q_i)
 void launch_mod_raise(int64_t* res, const int64_t* src, const LimbBatch& batch);
 
+}  // namespace fhert
+
+namespace fhert {
+inline cudaError_t counted_copy(void* dst, const void* src, size_t bytes, cudaMemcpyKind kind,
+                                cudaStream_t stream) {
+  Context* c = ctx_or_null();
+  if (c != nullptr) {
+    if (kind == cudaMemcpyHostToDevice) c->h2d_bytes += bytes;
+    else if (kind == cudaMemcpyDeviceToHost) c->d2h_bytes += bytes;
+  }
+  return cudaMemcpyAsync(dst, src, bytes, kind, stream);
+}
 }  // namespace fhert
 
 // ---- api.cu: multi-polynomial building blocks shared with bootstrap.cu ------

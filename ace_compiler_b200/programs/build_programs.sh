@@ -17,14 +17,16 @@ OUT="$HERE/_ref"
 mkdir -p "$OUT"
 
 build_one() {  # $1 generated file, $2 name
-  # generated files hold one very large function: the optimiser needs many
-  # minutes for it and the host code is only glue, so it is compiled plainly
+  # the host code of a generated file is only glue: no optimisation needed
   gcc -O0 -w -Werror=implicit-function-declaration -I"$REPO/include" \
       -include "$REPO/include/common/rtlib.h" -x c -c "$1" -o "$OUT/$2.o"
   gcc -O2 -I"$REPO/include" "$HERE/run_program.c" "$OUT/$2.o" -o "$OUT/$2" "$LIB" -lm \
       -Wl,-rpath,'$ORIGIN/../..'
+  # the same program as a shared object, for hosts that drive it in-process
+  gcc -O0 -w -fPIC -shared -I"$REPO/include" -include "$REPO/include/common/rtlib.h" \
+      -x c "$1" -x none -o "$OUT/$2.so" "$LIB" -lm -Wl,-rpath,'$ORIGIN/../..'
   rm -f "$OUT/$2.o"
-  echo "built $OUT/$2"
+  echo "built $OUT/$2 and $OUT/$2.so"
 }
 
 if [ $# -ge 2 ]; then

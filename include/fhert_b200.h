@@ -213,6 +213,8 @@ void Fhert_download(POLY poly, size_t first, size_t limbs, int64_t* host);
 void Fhert_sync(void);
 void* Fhert_stream(void);                /* cudaStream_t of the library */
 uint64_t Fhert_kernel_launches(void);    /* kernels queued since load */
+/* bytes copied host->device and device->host since the context was made */
+void     Fhert_transfer_bytes(uint64_t* h2d, uint64_t* d2h);
 /* Per-kernel device timing: between begin and end every kernel launch is
  * bracketed by CUDA events on the library stream; end waits for the stream and
  * writes one "name launches limbs total_ms" line per kernel into buf (limbs =
