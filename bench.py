@@ -463,6 +463,9 @@ def run_resnet20(args):
             "config": {"workload": R20_WORKLOAD, "ring_degree": DEGREE, "levels": R20_LEVELS,
                        "dnum": DNUM, "special_primes": R20_K,
                        "s_per_image": round(ms_graph / args.steps / 1e3, 4),
+                       "published_cpu_s_per_image": "1453.96 (one CPU thread, 60/56-bit primes; "
+                                                    "not this program's 51/46-bit parameters, "
+                                                    "so vs_baseline stays null)",
                        "setup_s": round(setup_s, 1),
                        "weight_plaintexts_resident": {"entries": stats[0].value,
                                                       "GiB": round(stats[1].value / 2 ** 30, 2)},
