@@ -441,15 +441,62 @@ void fhert_rescale_polys(Context* c, int npoly, int64_t* const res[2],
   launch_rescale_combine(ptr2(res[0], res[1]), ptr2(poly[0], poly[1]), ptr2(sc), l, bt);
 }
 
+// The two polynomials of a ciphertext are rescaled (or brought down from the
+// extended basis) by two calls in a row.  The device work of the first call
+// waits for the second and both run as one batch of launches; any other entry
+// point runs a waiting call on its own first (ctx()).
+static void pair_run(Context* c, int kind, int npoly, int64_t* const r[2],
+                     const int64_t* const x[2], size_t level, int p_limb, bool is_ntt) {
+  if (kind == 1) fhert_mod_down_polys(c, npoly, r, x, p_limb, nullptr, level, is_ntt);
+  else fhert_rescale_polys(c, npoly, r, x, level);
+}
+
+}  // extern "C"
+
+namespace fhert {
+void pair_flush(Context* c) {
+  auto w = c->pair_wait;
+  if (!w.kind) return;
+  c->pair_wait.kind   = 0;
+  int64_t*       r[2] = {w.res, nullptr};
+  const int64_t* x[2] = {w.src, nullptr};
+  pair_run(c, w.kind, 1, r, x, w.level, w.p_limb, w.is_ntt);
+}
+}  // namespace fhert
+
+extern "C" {
+
+static void pair_submit(int kind, int64_t* res, const int64_t* src, size_t level, int p_limb,
+                        bool is_ntt) {
+  Context* c = ctx_noflush();
+  if (c->hw_pending) {  // per-limb calls recorded since: everything older runs now
+    pair_flush(c);
+    hw_replay(c);
+  }
+  auto& w = c->pair_wait;
+  if (w.kind == kind && w.level == level && w.p_limb == p_limb && w.is_ntt == is_ntt &&
+      w.res != res && w.res != src && w.src != res) {
+    int64_t*       r[2] = {w.res, res};
+    const int64_t* x[2] = {w.src, src};
+    w.kind              = 0;
+    pair_run(c, kind, 2, r, x, level, p_limb, is_ntt);
+    return;
+  }
+  pair_flush(c);
+  w.kind   = kind;
+  w.res    = res;
+  w.src    = src;
+  w.level  = level;
+  w.p_limb = p_limb;
+  w.is_ntt = is_ntt;
+}
+
 POLY Rescale(POLY res, POLY poly) {
-  Context* c     = ctx();
-  size_t   level = poly->_num_primes;
+  size_t level = poly->_num_primes;
   FHERT_ASSERT(level >= 2, "Level of rescale opnd is too small");
   FHERT_ASSERT(res->_num_primes == level && res->_data, "Rescale: primes not match");
   FHERT_ASSERT(poly->_is_ntt, "Rescale: coefficient-form input is not supported");
-  int64_t*       r[2] = {res->_data, nullptr};
-  const int64_t* p[2] = {poly->_data, nullptr};
-  fhert_rescale_polys(c, 1, r, p, level);
+  pair_submit(2, res->_data, poly->_data, level, 0, true);
   res->_is_ntt     = true;
   res->_num_primes = level - 1;  // Modswitch(res, res)
   return res;
@@ -647,14 +694,11 @@ void fhert_mod_down_polys(Context* c, int npoly, int64_t* const res[2],
 }
 
 POLY Mod_down(POLY res, POLY poly) {
-  Context* c     = ctx();
-  size_t   level = poly->_num_primes;
-  if (res->_data == nullptr) Alloc_poly_data(res, c->N, level, 0);
-  FHERT_ASSERT(res->_num_primes == level && poly->_num_primes_p == (size_t)c->K,
+  size_t level = poly->_num_primes;
+  if (res->_data == nullptr) Alloc_poly_data(res, ctx()->N, level, 0);
+  FHERT_ASSERT(res->_num_primes == level && poly->_num_primes_p == (size_t)ctx_noflush()->K,
                "Mod_down: result size not match");
-  int64_t*       r[2] = {res->_data, nullptr};
-  const int64_t* x[2] = {poly->_data, nullptr};
-  fhert_mod_down_polys(c, 1, r, x, (int)p_offset(poly), nullptr, level, poly->_is_ntt);
+  pair_submit(1, res->_data, poly->_data, level, (int)p_offset(poly), poly->_is_ntt);
   res->_is_ntt = poly->_is_ntt;
   return res;
 }

@@ -15,7 +15,10 @@ static Context* g_ctx = nullptr;
 
 Context* ctx() {
   FHERT_ASSERT(g_ctx != nullptr, "no context: call Prepare_context first");
-  if (g_ctx->hw_pending) hw_replay(g_ctx);  // recorded per-limb operations run first
+  // deferred work runs first, oldest first: a waiting Mod_down / Rescale was
+  // queued before any per-limb call recorded after it
+  if (g_ctx->pair_wait.kind) pair_flush(g_ctx);
+  if (g_ctx->hw_pending) hw_replay(g_ctx);
   return g_ctx;
 }
 Context* ctx_noflush() {

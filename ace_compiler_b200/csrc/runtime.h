@@ -138,6 +138,16 @@ struct Context {
   struct HwQueue* hw_queue   = nullptr;
   bool            hw_pending = false;
   uint64_t        hw_batched_limbs = 0;
+  // a Mod_down / Rescale whose device work waits for its sibling (the second
+  // polynomial of the same ciphertext usually follows at once); see api.cu
+  struct {
+    int            kind = 0;  // 0 none, 1 Mod_down, 2 Rescale
+    int64_t*       res  = nullptr;
+    const int64_t* src  = nullptr;
+    size_t         level = 0;
+    int            p_limb = 0;
+    bool           is_ntt = true;
+  } pair_wait;
   // bytes moved between host and device since the context was made
   uint64_t h2d_bytes = 0, d2h_bytes = 0;
 
@@ -223,6 +233,7 @@ enum HwKind : uint8_t {
 bool hw_record(Context* c, HwKind kind, int64_t* res, const int64_t* a, const int64_t* b,
                const uint32_t* table, int64_t scalar, int prime);
 void hw_replay(Context* c);   // run everything recorded so far
+void pair_flush(Context* c);  // run a waiting Mod_down / Rescale on its own (api.cu)
 void hw_release(Context* c);
 
 // ---- data_file.cu ----
