@@ -219,12 +219,8 @@ def run_primitives(args):
             fn()
         e1.record(stream)
         barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+        from ace_compiler_b200 import parallel
+        return parallel.slowest_rank([e0.elapsed_time(e1)], device="cuda")[0]
 
     for _ in range(args.warmup):
         step_resident()
@@ -400,12 +396,10 @@ def run_resnet20(args):
     ms_graph = sum(a.elapsed_time(b) for a, b in events)
     launches = lib.Fhert_kernel_launches() - launches0
     h2d1, d2h1 = transfer()
-    if world > 1:
-        t = torch.tensor([ms_total, ms_graph], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, ms_graph = float(t[0].item()), float(t[1].item())
-    value = args.steps * world / (ms_graph * 1e-3)
-    e2e_value = args.steps * world / (ms_total * 1e-3)
+    from ace_compiler_b200 import parallel
+    ms_total, ms_graph = parallel.slowest_rank([ms_total, ms_graph], device="cuda")
+    value = parallel.job_throughput(args.steps, world, ms_graph)
+    e2e_value = parallel.job_throughput(args.steps, world, ms_total)
 
     # per-kernel device times of one more image (outside the timed region)
     buf = C.create_string_buffer(1 << 16)
