@@ -172,6 +172,22 @@ SIGNATURES = {
     "Poly_level": (C.c_size_t, [POLY]),
     "Num_p": (C.c_size_t, [POLY]),
     "Num_alloc": (C.c_size_t, [POLY]),
+    "Rotate_batch_ciph": (None, [CIPHER, CIPHER, C.POINTER(C.c_int32), C.c_uint32]),
+    "Add_plain": (CIPHER, [CIPHER, CIPHER, PLAIN]),
+    "Mul_plain": (CIPHER, [CIPHER, CIPHER, PLAIN]),
+    "Modswitch_ciph": (None, [CIPHER]),
+    "Upscale_ciph": (CIPHER, [CIPHER, CIPHER, C.c_uint32]),
+    "Downscale_ciph": (CIPHER, [CIPHER, CIPHER, C.c_uint32]),
+    "Raise_mod": (CIPHER, [CIPHER, CIPHER, C.c_uint32]),
+    "Mul_mono_ciph": (CIPHER, [CIPHER, CIPHER, C.c_uint32]),
+    "Print_cipher_msg": (None, [C.c_void_p, C.c_char_p, CIPHER, C.c_uint32]),
+    "Dump_cipher_msg": (None, [C.c_char_p, CIPHER, C.c_uint32]),
+    "Alloc_polys": (POLY, [C.c_uint32, C.c_uint32, C.c_size_t, C.c_size_t]),
+    "Free_polys": (None, [POLY]),
+    "Init_poly_by_opnd": (POLY, [POLY, POLY, POLY, C.c_bool]),
+    "Swk_c0": (POLY, [POLY, C.c_size_t, C.c_bool, C.c_int32]),
+    "Swk_c1": (POLY, [POLY, C.c_size_t, C.c_bool, C.c_int32]),
+    "Precomp": (POLY, [POLY, C.c_size_t, POLY]),
     "Bootstrap": (CIPHER, [CIPHER, CIPHER, C.c_uint32]),
     "Bootstrap_precom": (None, [C.c_uint32]),
     "Fhert_bootstrap_rotations": (C.c_size_t, [C.c_uint32, C.POINTER(C.c_int32), C.c_size_t]),

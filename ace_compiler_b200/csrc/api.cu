@@ -881,18 +881,16 @@ CIPHER3 Mul_ciph3(CIPHER3 res, CIPHER a, CIPHER b) {
 // out0/out1 receive level limbs; add0/add1 (optional) are added to them, which
 // folds the "+ c0" of a rotation and the "+ c0, + c1" of a relinearisation
 // into the last kernel.  About a dozen launches regardless of the digit count.
-void fhert_switch_key(Context* c, int64_t* out0, int64_t* out1, const int64_t* in, size_t level,
-                       SW_KEY swk, const int64_t* add0, const int64_t* add1) {
-  const uint32_t n     = c->N;
-  const int      K     = c->K;
-  const int      parts = (int)std::min<size_t>((level + c->alpha - 1) / c->alpha, c->dnum);
-  FHERT_ASSERT(parts <= kMaxParts, "too many digits");
-  const size_t ext_limbs = level + K;
-  int64_t*     buf       = nullptr;  // [parts] extended digits, then two accumulators
-  CUDA_CHECK(cudaMallocAsync(&buf, (size_t)(parts + 2) * ext_limbs * n * sizeof(int64_t), c->stream));
-  int64_t* acc0 = buf + (size_t)parts * ext_limbs * n;
+// Key switch of `in` whose digits were already raised into `digits`
+// (parts extended polynomials of level + K limbs each).
+void fhert_switch_key_raised(Context* c, int64_t* out0, int64_t* out1, const int64_t* in,
+                             const int64_t* digits, int parts, size_t level, SW_KEY swk,
+                             const int64_t* add0, const int64_t* add1) {
+  const uint32_t n         = c->N;
+  const size_t   ext_limbs = level + c->K;
+  int64_t*       acc0      = nullptr;
+  CUDA_CHECK(cudaMallocAsync(&acc0, 2 * ext_limbs * n * sizeof(int64_t), c->stream));
   int64_t* acc1 = acc0 + ext_limbs * n;
-  fhert_raise_parts(c, in, true, level, 0, parts, buf, ext_limbs, (int)level);
   InnerArgs args;
   std::memset(&args, 0, sizeof(args));
   args.parts      = parts;
@@ -903,7 +901,7 @@ void fhert_switch_key(Context* c, int64_t* out0, int64_t* out1, const int64_t* i
   args.acc_p_limb = (int)level;
   args.in         = reinterpret_cast<const u64*>(in);  // digits' own limbs come from the input
   for (int j = 0; j < parts; j++) {
-    args.ext_ptr[j] = reinterpret_cast<const u64*>(buf + (size_t)j * ext_limbs * n);
+    args.ext_ptr[j] = reinterpret_cast<const u64*>(digits + (size_t)j * ext_limbs * n);
     args.key0[j]    = reinterpret_cast<const u64*>(swk->_parts[j]._p0._data);
     args.key1[j]    = reinterpret_cast<const u64*>(swk->_parts[j]._p1._data);
   }
@@ -914,7 +912,19 @@ void fhert_switch_key(Context* c, int64_t* out0, int64_t* out1, const int64_t* i
   const int64_t* x[2] = {acc0, acc1};
   const int64_t* a[2] = {add0, add1};
   fhert_mod_down_polys(c, 2, r, x, (int)level, a, level, true);
-  CUDA_CHECK(cudaFreeAsync(buf, c->stream));
+  CUDA_CHECK(cudaFreeAsync(acc0, c->stream));
+}
+
+void fhert_switch_key(Context* c, int64_t* out0, int64_t* out1, const int64_t* in, size_t level,
+                      SW_KEY swk, const int64_t* add0, const int64_t* add1) {
+  const int parts = (int)std::min<size_t>((level + c->alpha - 1) / c->alpha, c->dnum);
+  FHERT_ASSERT(parts <= kMaxParts, "too many digits");
+  const size_t ext_limbs = level + c->K;
+  int64_t*     digits    = nullptr;
+  CUDA_CHECK(cudaMallocAsync(&digits, (size_t)parts * ext_limbs * c->N * sizeof(int64_t), c->stream));
+  fhert_raise_parts(c, in, true, level, 0, parts, digits, ext_limbs, (int)level);
+  fhert_switch_key_raised(c, out0, out1, in, digits, parts, level, swk, add0, add1);
+  CUDA_CHECK(cudaFreeAsync(digits, c->stream));
 }
 
 CIPHER Relin(CIPHER res, CIPHER3 ciph) {
@@ -969,6 +979,35 @@ static CIPHER rotate_with_key(CIPHER res, CIPHER ciph, int32_t rot_idx, uint32_t
                       auto_table(c, k), both_polys(one));
   CUDA_CHECK(cudaFreeAsync(t, c->stream));
   return res;
+}
+
+// cipher.c:460-481: several rotations of one ciphertext; its digits are raised
+// once and shared by all of them
+void Rotate_batch_ciph(CIPHER res_arr, CIPHER ciph, const int32_t* rot_idx, uint32_t count) {
+  if (count == 0) return;
+  Context* c     = ctx();
+  size_t   level = Level(ciph), words = level * c->N, ext_limbs = level + c->K;
+  const int parts = (int)std::min<size_t>((level + c->alpha - 1) / c->alpha, c->dnum);
+  int64_t *digits = nullptr, *t = nullptr;
+  CUDA_CHECK(cudaMallocAsync(&digits, (size_t)parts * ext_limbs * c->N * sizeof(int64_t), c->stream));
+  CUDA_CHECK(cudaMallocAsync(&t, 2 * words * sizeof(int64_t), c->stream));
+  fhert_raise_parts(c, ciph->_c1_poly._data, true, level, 0, parts, digits, ext_limbs, (int)level);
+  for (uint32_t i = 0; i < count; i++) {
+    CIPHER out = &res_arr[i];
+    FHERT_ASSERT(out != ciph, "Rotate_batch_ciph cannot work in place");
+    if (rot_idx[i] == 0) {
+      Copy_ciph(out, ciph);
+      continue;
+    }
+    fhert_switch_key_raised(c, t, t + words, ciph->_c1_poly._data, digits, parts, level,
+                            Swk(true, rot_idx[i]), ciph->_c0_poly._data, nullptr);
+    init_ciph(out, c->N, level, 0, ciph->_scaling_factor, ciph->_sf_degree, ciph->_slots);
+    LimbBatch one = poly_batch(c, &out->_c0_poly, &out->_c0_poly, nullptr, level, 0);
+    launch_automorphism(ptr2(out->_c0_poly._data, out->_c1_poly._data), ptr2(t, t + words),
+                        auto_table(c, auto_index_for(c, rot_idx[i])), both_polys(one));
+  }
+  CUDA_CHECK(cudaFreeAsync(t, c->stream));
+  CUDA_CHECK(cudaFreeAsync(digits, c->stream));
 }
 
 CIPHER Rotate_ciph(CIPHER res, CIPHER ciph, int32_t rot_idx) {

@@ -426,7 +426,7 @@ void keygen(Context* c, Precom* pre) {
 
 }  // namespace
 
-namespace {
+namespace fhert {
 
 // ---------------------------------------------------------------------------
 // ciphertext helpers used by the evaluation below (ckks/src/evaluator.c)
@@ -541,13 +541,36 @@ void mul_monomial(Context* c, CIPHER res, CIPHER a, uint32_t power) {
   Free_poly_data(&mono);
 }
 
+// bootstrap.c:1607-1632, cipher.c:417-446: down to scaling degree 1, keep only
+// the q_0 residues, lift them to the first raise_level primes
+void raise_from_level0(Context* c, CIPHER res, CIPHER ciph, uint32_t raise_level) {
+  const uint32_t n = c->N;
+  Ct low;
+  Copy_ciph(low.p(), ciph);
+  while (low.v._sf_degree > 1) Rescale_ciph(low.p(), low.p());
+  set_level(low.p(), 1);
+  Conv_ntt2poly_inplace(&low.v._c0_poly);
+  Conv_ntt2poly_inplace(&low.v._c1_poly);
+  ensure_poly(&res->_c0_poly, n, raise_level, 0);
+  ensure_poly(&res->_c1_poly, n, raise_level, 0);
+  res->_scaling_factor = low.v._scaling_factor;
+  res->_sf_degree      = low.v._sf_degree;
+  res->_slots          = ciph->_slots;
+  for (POLY dst : {&res->_c0_poly, &res->_c1_poly}) {
+    POLY src = dst == &res->_c0_poly ? &low.v._c0_poly : &low.v._c1_poly;
+    launch_mod_raise(dst->_data, src->_data, poly_batch(c, dst, dst, nullptr, raise_level, 0));
+    dst->_is_ntt = false;
+    Conv_poly2ntt_inplace(dst);
+  }
+}
+
 // evaluator.c:401-409
 void mod_switch(CIPHER ct) {
   FHERT_ASSERT(ct->_c0_poly._num_primes >= 2, "polynomial level is too small to support modswitch");
   set_level(ct, ct->_c0_poly._num_primes - 1);
 }
 
-}  // namespace
+}  // namespace fhert
 
 namespace {
 
@@ -1083,26 +1106,9 @@ void bootstrap_impl(Context* c, CIPHER res, CIPHER ciph, uint32_t level_after, P
   const double sf  = std::pow(2.0, (double)c->sf_bits);
   const int    deg = (int)std::round(std::log2((double)c->primes[0] / sf));
 
-  // down to scaling degree 1, keep only the q_0 limb, raise it to every prime
-  Ct low;
-  Copy_ciph(low.p(), ciph);
-  while (low.v._sf_degree > 1) Rescale_ciph(low.p(), low.p());
-  set_level(low.p(), 1);  // only the q_0 residues are used
-  Conv_ntt2poly_inplace(&low.v._c0_poly);
-  Conv_ntt2poly_inplace(&low.v._c1_poly);
   const uint32_t raise_level = level_after + bts_depth;
   Ct raised;
-  ensure_poly(&raised.v._c0_poly, n, raise_level, 0);
-  ensure_poly(&raised.v._c1_poly, n, raise_level, 0);
-  raised.v._scaling_factor = low.v._scaling_factor;
-  raised.v._sf_degree      = low.v._sf_degree;
-  raised.v._slots          = slots;
-  for (POLY dst : {&raised.v._c0_poly, &raised.v._c1_poly}) {
-    POLY src = dst == &raised.v._c0_poly ? &low.v._c0_poly : &low.v._c1_poly;
-    launch_mod_raise(dst->_data, src->_data, poly_batch(c, dst, dst, nullptr, raise_level, 0));
-    dst->_is_ntt = false;
-    Conv_poly2ntt_inplace(dst);
-  }
+  raise_from_level0(c, raised.p(), ciph, raise_level);
 
   Ct enc;
   if (slots == m / 4) {

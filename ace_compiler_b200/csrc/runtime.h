@@ -243,6 +243,15 @@ bool pt_cache_owns(const void* data);  // limb storage lent out by the plaintext
 // builds the linear-transform plaintexts and the rotation / conjugation keys
 // for `slots` (0 = N/2) when the context is deep enough (ckks_context.c:239-262)
 void prepare_bootstrap(Context* c, uint32_t slots);
+// ciphertext-level pieces shared with ciph_api.cu (evaluator.c:113-286, 401-409)
+void mul_const(Context* c, CIPHER res, CIPHER a, double value);
+void add_const(Context* c, CIPHER res, CIPHER a, double value);
+void mul_integer(Context* c, CIPHER res, CIPHER a, uint64_t power);
+void mul_monomial(Context* c, CIPHER res, CIPHER a, uint32_t power);
+void mod_switch(CIPHER ct);
+void raise_from_level0(Context* c, CIPHER res, CIPHER ciph, uint32_t raise_level);
+void shape_like(Context* c, CIPHER res, CIPHER a, double sf, uint32_t sf_degree);
+LimbBatch ct_batch(Context* c, CIPHER res, CIPHER a);
 void free_bootstrap(Context* c);
 
 // ---- context.cu ----

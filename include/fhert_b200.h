@@ -377,6 +377,26 @@ CIPHER  Rescale_ciph(CIPHER res, CIPHER ciph);          /* evaluator.c:344 */
 CIPHER  Rotate_ciph(CIPHER res, CIPHER ciph, int32_t rot_idx); /* evaluator.c:503-530 */
 CIPHER  Conjugate_ciph(CIPHER res, CIPHER ciph);        /* evaluator.c:568 */
 
+void    Rotate_batch_ciph(CIPHER res_arr, CIPHER ciph, const int32_t* rot_idx,
+                          uint32_t count);                  /* cipher.c:460-481, digits raised once */
+CIPHER  Add_plain(CIPHER res, CIPHER ciph, PLAIN plain);    /* evaluator.c:98 */
+CIPHER  Mul_plain(CIPHER res, CIPHER ciph, PLAIN plain);    /* evaluator.c:192 */
+void    Modswitch_ciph(CIPHER ciph);                        /* evaluator.c:401 */
+CIPHER  Upscale_ciph(CIPHER res, CIPHER ciph, uint32_t mod_size);    /* evaluator.c:364 */
+CIPHER  Downscale_ciph(CIPHER res, CIPHER ciph, uint32_t waterline); /* evaluator.c:380 */
+CIPHER  Raise_mod(CIPHER res, CIPHER ciph, uint32_t mod_size);       /* cipher.c:417 */
+CIPHER  Mul_mono_ciph(CIPHER res, CIPHER ciph, uint32_t power);      /* evaluator.c:260 */
+void    Print_cipher_msg(FILE* fp, const char* name, CIPHER ciph, uint32_t len);
+void    Dump_cipher_msg(const char* name, CIPHER ciph, uint32_t len);
+
+/* Polynomial arrays and views (include/poly/rns_poly.h:169-245, include/ckks/key.h:94-118) */
+POLY_ARR Alloc_polys(uint32_t cnt, uint32_t degree, size_t num_q, size_t num_p);
+void     Free_polys(POLY_ARR polys);
+POLY     Init_poly_by_opnd(POLY res, POLY opnd1, POLY opnd2, bool is_ext);
+POLY     Swk_c0(POLY res, size_t size, bool is_rot, int32_t rot_idx);
+POLY     Swk_c1(POLY res, size_t size, bool is_rot, int32_t rot_idx);
+POLY_ARR Precomp(POLY_ARR res, size_t size, POLY input);   /* rns_poly.c:459 */
+
 /* Bootstrapping (ant/ckks/src/cipher.c:565-583, bootstrap.c:1549-1830): raises
  * an exhausted ciphertext back to level_after_bts levels (0 = as many as the
  * context allows) with the reference's level budget {3, 3}, cosine series and
