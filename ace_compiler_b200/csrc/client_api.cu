@@ -226,15 +226,11 @@ void encode_scalar(Context* c, PLAIN plain, double value, uint32_t sf_degree, ui
   const double delta = std::pow(2.0, (double)c->sf_bits), scale = std::pow(delta, sf_degree);
   init_plain(c, plain, level, scale, sf_degree);
   std::vector<int64_t> res = encode_value(c, value, level, scale, 0);
-  // fill: zero the limb, then add the scalar
+  // fill every limb with its residue: one clear, one launch for all limbs
   POLY p = &plain->_poly;
   CUDA_CHECK(cudaMemsetAsync(p->_data, 0, (size_t)level * c->N * sizeof(int64_t), c->stream));
-  for (uint32_t i = 0; i < level; i++) {
-    LimbBatch b;
-    b.count   = 1;
-    b.limb[0] = LimbRef{(uint16_t)i, 0, (uint16_t)i, (uint8_t)i, 0};
-    launch_elementwise(EW_ADD_SCALAR, ptr2(p->_data), ptr2(p->_data), ptr2(p->_data), res[i], b);
-  }
+  std::vector<u64> sc(res.begin(), res.end());
+  launch_scalars(false, ptr2(p->_data), ptr2(p->_data), sc.data(), q_batch(level));
   p->_is_ntt = true;
 }
 

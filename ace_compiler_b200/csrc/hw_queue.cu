@@ -17,7 +17,6 @@
 // waiting is given a fresh scratch limb instead (renaming); the last value of
 // such a limb is copied to its real address at the end of the replay.
 #include <algorithm>
-#include <unordered_map>
 #include <vector>
 
 #include "runtime.h"
@@ -35,6 +34,7 @@ struct HwItem {
   u64*            dst;
   const u64*      a;
   const u64*      b;
+  const u64*      c;
   const uint32_t* table;
   int64_t         scalar;
   uint32_t        prime;
@@ -65,6 +65,7 @@ hw_batch_kernel(const __grid_constant__ HwLaunch launch, const DevModulus* __res
     else if (KIND == HW_ADD_SCALAR) r = add_mod(it.a[i], sc, m.q);
     else if (KIND == HW_MUL_SCALAR) r = mul_mod(it.a[i], sc, m);
     else if (KIND == HW_ROTATE) r = it.a[__ldg(it.table + i)];
+    else if (KIND == HW_MAC3) r = add_mod(it.c[i], mul_mod(it.a[i], it.b[i], m), m.q);
     else r = it.a[i];
     it.dst[i] = r;
   }
@@ -75,26 +76,41 @@ struct Node {
   HwItem item;
   int    level;
   bool   dead;
+  int    src_writer[3];  // node that produced each operand, -1 = memory
+  u64*   src_addr[3];    // the operands' own addresses
+  int    readers;        // recorded operations that read this node's value
+  bool   superseded;     // a later recorded call overwrote the same address
 };
 
-struct Version {  // the newest value of one limb address
-  u64* phys;      // where that value lives (the address itself or a scratch limb)
-  int  writer;    // node that produces it, -1 = already in memory
+// One slot per limb address seen in the current recording.  As a program
+// address it tracks the newest value of that limb (Version part); as a place
+// in memory it tracks the latest waves that touch it (Usage part).  Slots are
+// stamped with the recording's epoch, so starting a new recording costs nothing.
+struct Slot {
+  u64*     key;
+  uint32_t epoch;
+  // Version part
+  u64* phys;          // where the newest value lives (the address itself or a scratch limb)
+  int  writer;        // node that produces it, -1 = already in memory
   int  writer_level;
-  int  readers;   // recorded operations that read it
+  int  readers;       // recorded operations that read it
+  // Usage part
+  int read_level;
+  int write_level;
 };
+typedef Slot Version;
+typedef Slot Usage;
 
-struct Usage {  // per physical limb: the latest waves that touch it
-  int read_level  = 0;
-  int write_level = 0;
-};
+constexpr int kTableLog = 16;
 
 }  // namespace
 
 struct HwQueue {
   std::vector<Node>                   nodes;
-  std::unordered_map<u64*, Version>   versions;  // by logical address
-  std::unordered_map<u64*, Usage>     usage;     // by physical address
+  std::vector<Slot>                   table = std::vector<Slot>((size_t)1 << kTableLog);
+  uint32_t                            epoch = 1;
+  int                                 used  = 0;
+  std::vector<u64*>                   renamed;   // addresses whose value went to scratch
   std::vector<u64*>                   arenas;
   int                                 arena_used = kArena;
   int                                 max_level  = 0;
@@ -124,11 +140,24 @@ u64* scratch_limb(Context* c, HwQueue* q) {
   return q->arenas.back() + (size_t)(q->arena_used++) * c->N;
 }
 
-Version& version_of(HwQueue* q, u64* addr) {
-  auto it = q->versions.find(addr);
-  if (it == q->versions.end()) it = q->versions.emplace(addr, Version{addr, -1, 0, 0}).first;
-  return it->second;
+Slot* find_slot(HwQueue* q, const u64* addr, bool create) {
+  const size_t mask = ((size_t)1 << kTableLog) - 1;
+  size_t h = (size_t)(((uintptr_t)addr >> 6) * 0x9E3779B97F4A7C15ull >> (64 - kTableLog));
+  for (;;) {
+    Slot& s = q->table[h];
+    if (s.epoch != q->epoch) {
+      if (!create) return nullptr;
+      s = Slot{const_cast<u64*>(addr), q->epoch, const_cast<u64*>(addr), -1, 0, 0, 0, 0};
+      q->used++;
+      return &s;
+    }
+    if (s.key == addr) return &s;
+    h = (h + 1) & mask;
+  }
 }
+
+Version& version_of(HwQueue* q, u64* addr) { return *find_slot(q, addr, true); }
+Usage&   usage_of(HwQueue* q, const u64* addr) { return *find_slot(q, addr, true); }
 
 void run_wave(Context* c, HwKind kind, const std::vector<const Node*>& wave) {
   for (size_t off = 0; off < wave.size(); off += kHwItems) {
@@ -150,6 +179,7 @@ void run_wave(Context* c, HwKind kind, const std::vector<const Node*>& wave) {
       HW_CASE(HW_MUL_SCALAR)
       HW_CASE(HW_ROTATE)
       HW_CASE(HW_COPY)
+      HW_CASE(HW_MAC3)
     }
 #undef HW_CASE
     prof_after(KID_HW_BATCH, l.count);
@@ -165,12 +195,39 @@ void hw_replay(Context* c) {
   HwQueue* q = c->hw_queue;
   if (q == nullptr || q->nodes.empty() || q->replaying) return;
   q->replaying = true;
+  // "tmp = a * b; d = x + tmp" with tmp read once, a and b untouched by the
+  // recording: one multiply-add; a product overwritten later in the same
+  // recording never goes to memory
+  auto untouched = [&](const Node& p, int t) {
+    if (p.src_writer[t] != -1) return false;
+    Slot* sl = find_slot(q, p.src_addr[t], false);
+    return sl == nullptr || sl->writer == -1;
+  };
+  for (Node& sum : q->nodes) {
+    if (sum.dead || sum.kind != HW_ADD) continue;
+    for (int s = 0; s < 2; s++) {
+      int w = sum.src_writer[s];
+      if (w < 0) continue;
+      Node& prod = q->nodes[w];
+      if (prod.dead || prod.kind != HW_MUL || prod.readers != 1 ||
+          prod.item.prime != sum.item.prime || !untouched(prod, 0) || !untouched(prod, 1))
+        continue;
+      sum.kind   = HW_MAC3;
+      sum.item.c = s == 0 ? sum.item.b : sum.item.a;
+      sum.item.a = prod.item.a;
+      sum.item.b = prod.item.b;
+      // a product that is still the last value of its address stays, for
+      // whoever reads that address after the replay
+      if (prod.superseded) prod.dead = true;
+      break;
+    }
+  }
   std::vector<const Node*> wave;
   std::vector<std::vector<const Node*>> by_level(q->max_level + 1);
   for (const Node& nd : q->nodes)
     if (!nd.dead) by_level[nd.level].push_back(&nd);
   for (int level = 1; level <= q->max_level; level++) {
-    for (int kind = 0; kind <= (int)HW_COPY; kind++) {
+    for (int kind = 0; kind <= (int)HW_MAC3; kind++) {
       wave.clear();
       for (const Node* nd : by_level[level])
         if (nd->kind == (HwKind)kind) wave.push_back(nd);
@@ -179,14 +236,16 @@ void hw_replay(Context* c) {
   }
   // values that ended up in scratch limbs go home
   std::vector<Node> home;
-  for (auto& kv : q->versions) {
-    if (kv.second.phys == kv.first) continue;
+  for (u64* addr : q->renamed) {
+    Slot* sl = find_slot(q, addr, false);
+    if (sl == nullptr || sl->phys == addr) continue;
     Node nd{};
-    nd.kind      = HW_COPY;
-    nd.item.dst  = kv.first;
-    nd.item.a    = kv.second.phys;
+    nd.kind       = HW_COPY;
+    nd.item.dst   = addr;
+    nd.item.a     = sl->phys;
     nd.item.prime = 0;
     home.push_back(nd);
+    sl->phys = addr;  // listed once even if renamed several times
   }
   if (!home.empty()) {
     wave.clear();
@@ -197,8 +256,9 @@ void hw_replay(Context* c) {
   q->arenas.clear();
   q->arena_used = kArena;
   q->nodes.clear();
-  q->versions.clear();
-  q->usage.clear();
+  q->renamed.clear();
+  q->epoch++;
+  q->used = 0;
   q->max_level = 0;
   q->replaying = false;
   c->hw_pending = false;
@@ -230,45 +290,56 @@ bool hw_record(Context* c, HwKind kind, int64_t* res, const int64_t* a, const in
   int  level     = 0;
   bool in_place  = false;
   const u64* phys[3] = {nullptr, nullptr, nullptr};
+  Slot*      seen[3] = {nullptr, nullptr, nullptr};
   for (int i = 0; i < 3; i++) {
+    nd.src_writer[i] = -1;
+    nd.src_addr[i]   = src[i];
     if (src[i] == nullptr) continue;
     Version& v = version_of(q, src[i]);
+    seen[i]    = &v;
     phys[i]    = v.phys;
     level      = std::max(level, v.writer_level);
+    nd.src_writer[i] = v.writer;
     if (src[i] == dst) in_place = true;
   }
+  nd.readers    = 0;
+  nd.superseded = false;
   level += 1;
   Version& dv = version_of(q, dst);
   u64*     out;
+  if (dv.writer >= 0) q->nodes[dv.writer].superseded = true;
   if (!in_place && dv.readers > 0) {
     out = scratch_limb(c, q);  // earlier readers keep the old value
   } else {
     out = dv.phys;
     if (!in_place && dv.readers == 0 && dv.writer >= 0) q->nodes[dv.writer].dead = true;
-    Usage& u = q->usage[out];
+    Usage& u = out == dst ? dv : usage_of(q, out);
     level    = std::max(level, std::max(u.read_level, u.write_level) + 1);
   }
   for (int i = 0; i < 3; i++) {
     if (src[i] == nullptr) continue;
-    Version& v = version_of(q, src[i]);
+    Version& v = *seen[i];
     v.readers++;
-    Usage& u     = q->usage[v.phys];
+    if (v.writer >= 0) q->nodes[v.writer].readers++;
+    Usage& u     = v.phys == v.key ? v : usage_of(q, v.phys);
     u.read_level = std::max(u.read_level, level);
   }
   nd.item.dst = out;
   nd.item.a   = phys[0];
   nd.item.b   = phys[1];
   nd.level    = level;
-  q->usage[out].write_level = level;
-  Version& fresh    = version_of(q, dst);
+  (out == dst ? dv : usage_of(q, out)).write_level = level;
+  if (out != dst) q->renamed.push_back(dst);
+  Version& fresh    = dv;
   fresh.phys        = out;
   fresh.writer      = (int)q->nodes.size();
   fresh.writer_level = level;
   fresh.readers     = 0;
+  if (q->nodes.capacity() == 0) q->nodes.reserve(kMaxNodes + 8);
   q->nodes.push_back(nd);
   q->max_level  = std::max(q->max_level, level);
   c->hw_pending = true;
-  if ((int)q->nodes.size() >= kMaxNodes) {
+  if ((int)q->nodes.size() >= kMaxNodes || q->used > (1 << (kTableLog - 1))) {
     pair_flush(c);  // a waiting Mod_down / Rescale is older than anything recorded
     hw_replay(c);
   }

@@ -227,7 +227,8 @@ std::vector<int64_t> encode_value(Context* c, double value, uint32_t level, doub
 
 // ---- hw_queue.cu: deferred per-limb vector operations ----
 enum HwKind : uint8_t {
-  HW_ADD, HW_SUB, HW_MUL, HW_MULADD, HW_ADD_SCALAR, HW_MUL_SCALAR, HW_ROTATE, HW_COPY
+  HW_ADD, HW_SUB, HW_MUL, HW_MULADD, HW_ADD_SCALAR, HW_MUL_SCALAR, HW_ROTATE, HW_COPY,
+  HW_MAC3  // res = c + a * b, made at replay from a product and the sum that consumes it
 };
 // records res = a (kind) b on one limb; false = recording is off, launch now
 bool hw_record(Context* c, HwKind kind, int64_t* res, const int64_t* a, const int64_t* b,
