@@ -469,10 +469,7 @@ extern "C" {
 static void pair_submit(int kind, int64_t* res, const int64_t* src, size_t level, int p_limb,
                         bool is_ntt) {
   Context* c = ctx_noflush();
-  if (c->hw_pending) {  // per-limb calls recorded since: everything older runs now
-    pair_flush(c);
-    hw_replay(c);
-  }
+  if (c->hw_pending) ctx();  // per-limb calls recorded since: everything older runs now
   auto& w = c->pair_wait;
   if (w.kind == kind && w.level == level && w.p_limb == p_limb && w.is_ntt == is_ntt &&
       w.res != res && w.res != src && w.src != res) {
@@ -482,7 +479,7 @@ static void pair_submit(int kind, int64_t* res, const int64_t* src, size_t level
     pair_run(c, kind, 2, r, x, level, p_limb, is_ntt);
     return;
   }
-  pair_flush(c);
+  if (w.kind) ctx();  // an unrelated call was waiting: it runs alone
   w.kind   = kind;
   w.res    = res;
   w.src    = src;

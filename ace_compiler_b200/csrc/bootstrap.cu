@@ -1058,11 +1058,15 @@ void linear_transform(Context* c, CIPHER result, CIPHER in, Precom* pre, bool en
   }
   Copy_ciph(result, in);
   if (encoding)
-    for (int s = end - 1; s > start - 1; s--)
+    for (int s = end - 1; s > start - 1; s--) {
       rotate_stage(c, result, plain[s], p, rot_in[s], rot_out[s], s, true, false);
+      trace_sum("c2s stage", result);
+    }
   else
-    for (int s = start; s < end; s++)
+    for (int s = start; s < end; s++) {
       rotate_stage(c, result, plain[s], p, rot_in[s], rot_out[s], s, false, false);
+      trace_sum("s2c stage", result);
+    }
   if (flag_rem) {
     int s = encoding ? stop : p.level_budget - flag_rem;
     rotate_stage(c, result, plain[s], p, rot_in[s], rot_out[s], s, encoding, true);
@@ -1115,9 +1119,12 @@ void bootstrap_impl(Context* c, CIPHER res, CIPHER ciph, uint32_t level_after, P
     linear_transform(c, enc.p(), raised.p(), pre, true);
     Ct conj, diff;
     Conjugate_ciph(conj.p(), enc.p());
+    trace_sum("conj", conj.p());
     Sub_ciph(diff.p(), enc.p(), conj.p());
     Add_ciph(enc.p(), enc.p(), conj.p());
+    trace_sum("sum", enc.p());
     mul_monomial(c, diff.p(), diff.p(), 3 * m / 4);
+    trace_sum("diff", diff.p());
     while (enc.v._sf_degree > 1) {
       Rescale_ciph(enc.p(), enc.p());
       Rescale_ciph(diff.p(), diff.p());

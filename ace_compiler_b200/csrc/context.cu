@@ -16,9 +16,14 @@ static Context* g_ctx = nullptr;
 Context* ctx() {
   FHERT_ASSERT(g_ctx != nullptr, "no context: call Prepare_context first");
   // deferred work runs first, oldest first: a waiting Mod_down / Rescale was
-  // queued before any per-limb call recorded after it
-  if (g_ctx->pair_wait.kind) pair_flush(g_ctx);
-  if (g_ctx->hw_pending) hw_replay(g_ctx);
+  // queued before any per-limb call recorded after it.  The launches of that
+  // work come back through here; they must not start the younger work early.
+  if ((g_ctx->pair_wait.kind || g_ctx->hw_pending) && !g_ctx->draining) {
+    g_ctx->draining = true;
+    if (g_ctx->pair_wait.kind) pair_flush(g_ctx);
+    if (g_ctx->hw_pending) hw_replay(g_ctx);
+    g_ctx->draining = false;
+  }
   return g_ctx;
 }
 Context* ctx_noflush() {

@@ -339,10 +339,8 @@ bool hw_record(Context* c, HwKind kind, int64_t* res, const int64_t* a, const in
   q->nodes.push_back(nd);
   q->max_level  = std::max(q->max_level, level);
   c->hw_pending = true;
-  if ((int)q->nodes.size() >= kMaxNodes || q->used > (1 << (kTableLog - 1))) {
-    pair_flush(c);  // a waiting Mod_down / Rescale is older than anything recorded
-    hw_replay(c);
-  }
+  if ((int)q->nodes.size() >= kMaxNodes || q->used > (1 << (kTableLog - 1)))
+    ctx();  // runs a waiting Mod_down / Rescale (older) and then the recording
   return true;
 }
 

@@ -221,7 +221,35 @@ void Init_ciph3_up_scale(CIPHER3 res, CIPHER ciph1, CIPHER ciph2) {
                   ciph1->_sf_degree + ciph2->_sf_degree, ciph->_slots);
 }
 
+// FHERT_TRACE_SUMS=1: every Copy_ciph prints a checksum of the residues it
+// copies (a debugging aid for comparing two runs operator by operator, in the
+// spirit of the reference's trace file; drains the device each time)
+}  // extern "C"
+namespace fhert {
+void trace_sum(const char* what, CIPHER ciph) {
+  static int on = -1, serial = 0;
+  if (on < 0) {
+    const char* e = std::getenv("FHERT_TRACE_SUMS");
+    on            = e != nullptr && e[0] != '\0' && e[0] != '0';
+  }
+  if (!on) return;
+  size_t level = ciph->_c0_poly._num_primes, n = ciph->_c0_poly._ring_degree;
+  std::vector<int64_t> host(level * n);
+  uint64_t sum[2] = {0, 0};
+  int      k      = 0;
+  for (POLY p : {&ciph->_c0_poly, &ciph->_c1_poly}) {
+    Fhert_download(p, 0, level, host.data());
+    for (size_t i = 0; i < host.size(); i++) sum[k] = sum[k] * 1099511628211ull + (uint64_t)host[i];
+    k++;
+  }
+  std::fprintf(stderr, "[FHERT_SUM] %d %s level %zu deg %u %016llx %016llx\n", serial++, what, level,
+               ciph->_sf_degree, (unsigned long long)sum[0], (unsigned long long)sum[1]);
+}
+}  // namespace fhert
+extern "C" {
+
 void Copy_ciph(CIPHER res, CIPHER ciph) {
+  trace_sum("copy", ciph);
   init_from_ciph(res, ciph, ciph->_scaling_factor, ciph->_sf_degree);
   Copy_poly(&res->_c0_poly, &ciph->_c0_poly);
   Copy_poly(&res->_c1_poly, &ciph->_c1_poly);

@@ -137,6 +137,7 @@ struct Context {
   // recorded per-limb vector operations awaiting replay (hw_queue.cu)
   struct HwQueue* hw_queue   = nullptr;
   bool            hw_pending = false;
+  bool            draining   = false;  // deferred work is being launched right now
   uint64_t        hw_batched_limbs = 0;
   // a Mod_down / Rescale whose device work waits for its sibling (the second
   // polynomial of the same ciphertext usually follows at once); see api.cu
@@ -236,6 +237,10 @@ bool hw_record(Context* c, HwKind kind, int64_t* res, const int64_t* a, const in
 void hw_replay(Context* c);   // run everything recorded so far
 void pair_flush(Context* c);  // run a waiting Mod_down / Rescale on its own (api.cu)
 void hw_release(Context* c);
+
+// ---- program_api.cu ----
+// FHERT_TRACE_SUMS=1: prints a checksum of the ciphertext's residues to stderr
+void trace_sum(const char* what, CIPHER ciph);
 
 // ---- data_file.cu ----
 bool pt_cache_owns(const void* data);  // limb storage lent out by the plaintext cache

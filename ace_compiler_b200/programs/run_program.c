@@ -6,7 +6,9 @@
  * wall-clock around each stage with the device drained.
  *
  * usage: run_program [--shape n,c,h,w] [--seed s] [--images k] [--input name]
- *                    [--output name] [--values m]
+ *                    [--output name] [--values m] [--pin p]
+ * --pin p seeds the library's key / encryption randomness (Fhert_seed) so that two runs
+ * produce the same ciphertexts and therefore the same logits, bit for bit.
  * prints one JSON line per image:
  *   {"image": i, "encrypt_s": .., "infer_s": .., "decrypt_s": .., "logits": [..]}
  * and a final line {"setup_s": .., "images": k, "mean_infer_s": ..}.
@@ -38,6 +40,7 @@ int main(int argc, char** argv) {
   size_t      shape[4] = {1, 3, 32, 32};
   uint64_t    seed     = 1;
   int         images = 1, values = 10;
+  long        pin    = -1;
   const char *in_name = "input", *out_name = "output";
   for (int i = 1; i + 1 < argc; i += 2) {
     if (!strcmp(argv[i], "--shape"))
@@ -45,8 +48,14 @@ int main(int argc, char** argv) {
     else if (!strcmp(argv[i], "--seed")) seed = strtoull(argv[i + 1], NULL, 10);
     else if (!strcmp(argv[i], "--images")) images = atoi(argv[i + 1]);
     else if (!strcmp(argv[i], "--values")) values = atoi(argv[i + 1]);
+    else if (!strcmp(argv[i], "--pin")) pin = atol(argv[i + 1]);
     else if (!strcmp(argv[i], "--input")) in_name = argv[i + 1];
     else if (!strcmp(argv[i], "--output")) out_name = argv[i + 1];
+  }
+  if (pin >= 0) {
+    uint32_t words[16];
+    for (int k = 0; k < 16; k++) words[k] = (uint32_t)(pin * 2654435761u + 40503u * k);
+    Fhert_seed(words, 0, 1700000000000000ll + pin);
   }
   double t0 = now_s();
   Prepare_context();
@@ -70,7 +79,7 @@ int main(int argc, char** argv) {
     printf("{\"image\": %d, \"encrypt_s\": %.6f, \"infer_s\": %.6f, \"decrypt_s\": %.6f, "
            "\"launches\": %llu, \"logits\": [",
            img, b - a, c - b, d - c, (unsigned long long)Fhert_kernel_launches());
-    for (int k = 0; k < values; k++) printf("%s%.6f", k ? ", " : "", out[k]);
+    for (int k = 0; k < values; k++) printf("%s%.17g", k ? ", " : "", out[k]);
     printf("]}\n");
     fflush(stdout);
     free(out);

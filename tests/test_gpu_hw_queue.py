@@ -127,3 +127,26 @@ def test_key_switch_idiom_is_merged(gpu):
     assert np.array_equal(gpu.download(tmp)[0], last.astype(np.int64))
     for p in (key, dig, acc, tmp):
         gpu.free(p)
+
+
+def test_waiting_rescale_runs_before_younger_limb_calls(gpu):
+    """A lone Rescale waits for a sibling; per-limb calls recorded after it read
+    its result, so the drain must run the Rescale first."""
+    lib = gpu.lib
+    rng = np.random.default_rng(31)
+    level = 4
+    data = np.stack([rng.integers(0, p, N, dtype=np.int64) for p in gpu.primes[:level]])
+    src = gpu.new_poly(level, data=data)
+    ref_out = gpu.new_poly(level)
+    lib.Rescale(ref_out, src)
+    want = gpu.download(ref_out)          # the download drains: the plain result
+    out = gpu.new_poly(level)
+    acc = gpu.new_poly(level - 1)
+    gpu.upload(acc, np.zeros((level - 1, N), np.int64))
+    lib.Rescale(out, src)                 # waits
+    for i in range(level - 1):            # recorded, reads the waiting call's result
+        lib.Hw_modadd(gpu.limb_ptr(acc, i), gpu.limb_ptr(acc, i), gpu.limb_ptr(out, i),
+                      gpu.modulus(i), N)
+    assert np.array_equal(gpu.download(acc), want)
+    for p in (src, ref_out, out, acc):
+        gpu.free(p)
