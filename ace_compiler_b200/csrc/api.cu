@@ -117,6 +117,14 @@ void Prepare_context(void) {
   if (ctx_or_null()) return;
   CKKS_PARAMS* p = Get_context_params();
   FHERT_ASSERT(p != nullptr, "Get_context_params returned no parameters");
+  // FHERT_PIN=<n> fixes the key / encryption randomness of a program that does
+  // not call Fhert_seed itself, so that two runs can be compared bit for bit
+  if (const char* pin = std::getenv("FHERT_PIN")) {
+    uint32_t words[16];
+    long     v = std::atol(pin);
+    for (int k = 0; k < 16; k++) words[k] = (uint32_t)(v * 2654435761u + 40503u * k);
+    Fhert_seed(words, 0, 1700000000000000ll + v);
+  }
   Context* c = create_context(p);
   for (size_t i = 0; i < p->_num_rot_idx; i++) auto_index_for(c, p->_rot_idxs[i]);
   const char* skip = std::getenv("FHERT_SKIP_KEYGEN");

@@ -255,6 +255,10 @@ static T* upload(const std::vector<T>& v) {
   if (v.empty()) return d;
   CUDA_CHECK(cudaMalloc(&d, v.size() * sizeof(T)));
   CUDA_CHECK(cudaMemcpy(d, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice));
+  // a copy from pageable memory may still be in flight when cudaMemcpy returns,
+  // and the library stream is not ordered against the default stream: tables
+  // built on first use are read by the very next kernel
+  CUDA_CHECK(cudaStreamSynchronize(0));
   return d;
 }
 

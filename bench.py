@@ -386,12 +386,14 @@ def run_resnet20(args):
     launches0, (h2d0, d2h0) = lib.Fhert_kernel_launches(), transfer()
     events = []
     E0, E1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    cpu0 = time.process_time()
     with ClockSampler(local) as clocks:
         E0.record(stream)
         for _ in range(args.steps):
             logits = one_image(events)
         E1.record(stream)
         barrier()
+    host_cpu_s = (time.process_time() - cpu0) / args.steps
     ms_total = E0.elapsed_time(E1)
     ms_graph = sum(a.elapsed_time(b) for a, b in events)
     launches = lib.Fhert_kernel_launches() - launches0
@@ -461,6 +463,7 @@ def run_resnet20(args):
                                                     "not this program's 51/46-bit parameters, "
                                                     "so vs_baseline stays null)",
                        "setup_s": round(setup_s, 1),
+                       "host_cpu_s_per_image": round(host_cpu_s, 3),
                        "weight_plaintexts_resident": {"entries": stats[0].value,
                                                       "GiB": round(stats[1].value / 2 ** 30, 2)},
                        "l2": "inputs_larger_than_l2 (keys and cached plaintexts, tens of GiB, "

@@ -44,3 +44,21 @@ def test_example_program(name):
         return
     assert "SUCESS!" in run.stdout, tail
     assert "FAILED" not in run.stdout, tail
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", [n for n in NAMES if n.split("_")[-1] in
+                                  ("conv2d", "gemm", "relu", "rotate", "relin", "bootstrap")])
+def test_recording_is_transparent(name):
+    """With pinned randomness, the checksums of every ciphertext the program
+    copies are the same whether the per-limb calls are recorded and merged or
+    launched one by one."""
+    exe = os.path.join(EXAMPLES, name)
+    traces = []
+    for eager in ("0", "1"):
+        env = dict(os.environ, FHERT_PIN="3", FHERT_TRACE_SUMS="1", FHERT_EAGER_HW=eager)
+        run = subprocess.run([exe], capture_output=True, text=True, timeout=600, env=env)
+        assert run.returncode == 0, run.stderr[-2000:]
+        traces.append([ln for ln in run.stderr.splitlines() if ln.startswith("[FHERT_SUM]")])
+    assert len(traces[0]) > 0
+    assert traces[0] == traces[1]
