@@ -219,6 +219,8 @@ SIGNATURES = {
     "Validate_impl": (None, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.c_uint32, C.c_int32]),
     "Validate_value_range": (None, [C.c_bool]),
     "Within_value_range": (C.c_bool, [CIPHER, C.POINTER(C.c_double), C.c_uint32]),
+    "Fhert_tm_event": (None, [C.c_uint32, C.c_uint32, C.c_int]),
+    "Fhert_tm_report": (None, []),
     "Tm_start": (None, [C.c_char_p]),
     "Tm_taken": (None, [C.c_char_p]),
     "Level": (C.c_size_t, [CIPHER]),

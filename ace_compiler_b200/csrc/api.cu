@@ -157,6 +157,7 @@ void Prepare_context(void) {
 
 void Finalize_context(void) {
   if (ctx_or_null() == nullptr) return;
+  Fhert_tm_report();
   Pt_mgr_fini();
   destroy_context();
 }

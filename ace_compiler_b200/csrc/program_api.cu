@@ -327,6 +327,50 @@ void Validate_value_range(bool within_range) {
                  "Please set a higher level or increase the difference between q0 and sf.\n");
 }
 
+// ---- event timers of newer generated programs (common/linux/rtlib_timing.c)
+namespace {
+struct TmEvent {
+  uint64_t count = 0;
+  double   total = 0;
+};
+std::map<std::pair<uint32_t, uint32_t>, TmEvent>            g_tm_events;
+std::vector<std::pair<std::pair<uint32_t, uint32_t>, double>> g_tm_stack;
+const char* tm_target() {
+  static const char* t    = std::getenv("RTLIB_TIMING_OUTPUT");
+  return t != nullptr && t[0] != '\0' ? t : nullptr;
+}
+}  // namespace
+
+void Fhert_tm_event(uint32_t id, uint32_t sub, int end) {
+  if (tm_target() == nullptr) return;
+  Fhert_sync();
+  double now = wall_seconds();
+  if (!end) {
+    g_tm_stack.push_back({{id, sub}, now});
+    return;
+  }
+  FHERT_ASSERT(!g_tm_stack.empty() && g_tm_stack.back().first == std::make_pair(id, sub),
+               "FATAL: RTM stack mismatch");
+  TmEvent& e = g_tm_events[{id, sub}];
+  e.count++;
+  e.total += now - g_tm_stack.back().second;
+  g_tm_stack.pop_back();
+}
+
+void Fhert_tm_report(void) {
+  const char* t = tm_target();
+  if (t == nullptr || g_tm_events.empty()) return;
+  FILE* fp = !std::strcmp(t, "stdout") ? stdout : (!std::strcmp(t, "stderr") ? stderr : std::fopen(t, "w"));
+  if (fp == nullptr) return;
+  std::fprintf(fp, "%-12s %-6s %10s %14s\n", "event", "sub", "count", "seconds");
+  for (auto& kv : g_tm_events)
+    std::fprintf(fp, "%-12u %-6u %10llu %14.6f\n", kv.first.first, kv.first.second,
+                 (unsigned long long)kv.second.count, kv.second.total);
+  if (fp != stdout && fp != stderr) std::fclose(fp);
+  else std::fflush(fp);
+  g_tm_events.clear();
+}
+
 // ---- timer (common/src/rt_stat.c:23-31); scripts parse this line format
 // FHERT_RT_STAT=0 silences the lines and skips the device drain they need
 static bool tm_enabled() {

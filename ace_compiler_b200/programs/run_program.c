@@ -22,6 +22,32 @@
 
 #include "common/rtlib.h"
 
+/* -DREFERENCE_RUNTIME builds the same driver against the reference CPU runtime
+ * (its own headers and library plus the test hooks of oracle/ref_hooks.c), so
+ * that a program can be run on both sides with the same pinned randomness,
+ * the same input and the same weight file, and the outputs compared. */
+#ifdef REFERENCE_RUNTIME
+void Ref_seed_prng(const uint32_t* seed, uint64_t counter);
+void Ref_set_fake_time(int64_t us);
+static void Fhert_sync(void) {}
+static unsigned long long Fhert_kernel_launches(void) { return 0; }
+static void Fhert_seed(const uint32_t* seed, uint64_t counter, int64_t fake_us) {
+  Ref_set_fake_time(fake_us);
+  Ref_seed_prng(seed, counter);
+}
+/* the program's own hook is renamed on the command line; this one swaps in
+ * the weight file named by FHERT_DATA_FILE, as the B200 runtime does itself */
+RT_DATA_INFO* Program_rt_data_info(void);
+RT_DATA_INFO* Get_rt_data_info(void) {
+  static RT_DATA_INFO info;
+  RT_DATA_INFO*       own = Program_rt_data_info();
+  if (own == NULL) return NULL;
+  info = *own;
+  if (getenv("FHERT_DATA_FILE")) info._file_name = getenv("FHERT_DATA_FILE");
+  return &info;
+}
+#endif
+
 static double now_s(void) {
   struct timespec ts;
   clock_gettime(CLOCK_MONOTONIC, &ts);

@@ -465,6 +465,20 @@ static inline void Validate(CIPHER ciph, double* msg, uint32_t len, int32_t epsi
   Validate_value_range(Within_value_range(ciph, msg, len));
 }
 
+/* Event timers that newer generated programs bracket their operators with
+ * (include/common/rtlib_timing.h:111-160; the ids are the compiler's event
+ * numbers and are only used as labels here).  They cost nothing unless
+ * RTLIB_TIMING_OUTPUT is set (stdout, stderr or a file name); then every
+ * event drains the device so that queued kernels are charged to it, and
+ * Finalize_context writes count and seconds per event. */
+void Fhert_tm_event(uint32_t id, uint32_t sub, int end);
+void Fhert_tm_report(void);
+#define RTLIB_TM_START(id, mark) Fhert_tm_event((id), 0, 0)
+#define RTLIB_TM_END(id, mark)   Fhert_tm_event((id), 0, 1)
+#define CMPLR_TM_START(id, s)    Fhert_tm_event((id), (s), 0)
+#define CMPLR_TM_END(id, s)      Fhert_tm_event((id), (s), 1)
+#define RTLIB_TM_REPORT()        Fhert_tm_report()
+
 /* per-operator timer; prints "[RT_STAT] <msg> takes <s> seconds." after
  * draining the stream, so queued kernels are charged to their operator */
 void Tm_start(const char* msg);

@@ -35,3 +35,33 @@ for src in "$EG"/eg_fhertlib_*.c; do
   fi
 done
 echo "built $built example programs in $OUT; not built: ${skipped[*]:-none}"
+
+# Twin builds of single-layer programs of the newer emit generation
+# (fhe-cmplr/rtlib/ant/dataset/conv_*): once against the B200 library, once
+# against the reference library, both with the driver
+# ace_compiler_b200/programs/run_program.c.  The GPU tests run both with the
+# same pinned randomness, input and weight file and compare the outputs.
+DATASET="$REF/fhe-cmplr/rtlib/ant/dataset"
+RT="$REF/fhe-cmplr/rtlib"
+REFLIB="$HERE/_ref/libFHErt_ant_prog.so"
+DRIVER="$REPO/ace_compiler_b200/programs/run_program.c"
+TW="$HERE/_ref/twins"
+mkdir -p "$TW"
+RINC=(-I"$HERE/shims" -I"$RT/include" -I"$RT/ant/include" -I"$RT/ant/util/include"
+      -I"$RT/ant/hal/include" -I"$RT/ant/poly/include" -I"$RT/ant/ckks/include"
+      -I"$REF/fhe-cmplr/include" -I"$REF/air-infra/include" -I"$REF/nn-addon/include")
+for name in conv_3x16x32x3 conv_16x16x32x3; do
+  src="$DATASET/${name}_pre.onnx.inc"
+  [ -f "$src" ] && [ -f "$REFLIB" ] || continue
+  gcc -O0 -w -Werror=implicit-function-declaration -I"$REPO/include" \
+      -include "$REPO/include/common/rtlib.h" -x c -c "$src" -o "$TW/$name.b200.o"
+  gcc -O2 -I"$REPO/include" "$DRIVER" "$TW/$name.b200.o" -o "$TW/$name.b200" "$LIB" -lm \
+      -Wl,-rpath,'$ORIGIN/../../../ace_compiler_b200'
+  gcc -O0 -w -std=gnu11 -DRTLIB_SUPPORT_LINUX -DOPENFHE_COMPAT -DNDEBUG "${RINC[@]}" \
+      -DGet_rt_data_info=Program_rt_data_info -include "$RT/include/common/rtlib.h" \
+      -x c -c "$src" -o "$TW/$name.ref.o"
+  gcc -O2 -std=gnu11 -DREFERENCE_RUNTIME -DRTLIB_SUPPORT_LINUX -DOPENFHE_COMPAT -DNDEBUG "${RINC[@]}" \
+      "$DRIVER" "$TW/$name.ref.o" -o "$TW/$name.ref" "$REFLIB" -lm -Wl,-rpath,'$ORIGIN/..'
+  rm -f "$TW/$name.b200.o" "$TW/$name.ref.o"
+  echo "built twins $TW/$name.{b200,ref}"
+done

@@ -50,6 +50,15 @@ build_variant() {  # $1 = suffix, rest = extra flags
   gcc -shared "$@" -o "$OUT/libFHErt_ant_ref$suf.so" "${objs[@]}" -lm \
       -Wl,--allow-shlib-undefined -Wl,-z,defs -Wl,-Bsymbolic
   echo "built $OUT/libFHErt_ant_ref$suf.so"
+  if [ -z "$suf" ]; then
+    # the same objects without the Python-facing harness (which answers the
+    # program hooks itself): compiled programs link against this one and keep
+    # their own Get_context_params, Main_graph ...
+    local prog=()
+    for o in "${objs[@]}"; do case "$o" in *ref_harness*) ;; *) prog+=("$o");; esac; done
+    gcc -shared -o "$OUT/libFHErt_ant_prog.so" "${prog[@]}" -lm -Wl,--allow-shlib-undefined
+    echo "built $OUT/libFHErt_ant_prog.so"
+  fi
 }
 
 build_variant ""

@@ -14,6 +14,7 @@ def declared_functions():
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     text = re.sub(r"typedef\s+(struct|enum)\s*\{.*?\}\s*\w+\s*;", "", text, flags=re.S)
     text = re.sub(r"enum\s*\{.*?\}\s*;", "", text, flags=re.S)
+    text = re.sub(r"^#define[^\n]*(\\\n[^\n]*)*", "", text, flags=re.M)  # macros are not symbols
     names = re.findall(r"\b([A-Z][A-Za-z0-9_]*)\s*\([^;{}]*\)\s*;", text)
     return sorted(set(names))
 
