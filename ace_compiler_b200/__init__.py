@@ -188,6 +188,12 @@ SIGNATURES = {
     "Swk_c0": (POLY, [POLY, C.c_size_t, C.c_bool, C.c_int32]),
     "Swk_c1": (POLY, [POLY, C.c_size_t, C.c_bool, C.c_int32]),
     "Precomp": (POLY, [POLY, C.c_size_t, POLY]),
+    "Fhert_shard_blocks": (None, [C.c_size_t, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "Fhert_shard_begin": (C.c_void_p, [C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_void_p]),
+    "Fhert_shard_mid": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int, C.c_void_p,
+                               C.c_void_p]),
+    "Fhert_shard_end": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int,
+                               C.c_void_p, C.c_void_p]),
     "Bootstrap": (CIPHER, [CIPHER, CIPHER, C.c_uint32]),
     "Bootstrap_precom": (None, [C.c_uint32]),
     "Fhert_bootstrap_rotations": (C.c_size_t, [C.c_uint32, C.POINTER(C.c_int32), C.c_size_t]),

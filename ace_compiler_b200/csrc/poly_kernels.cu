@@ -201,6 +201,7 @@ base_conv_kernel(ConvArgs args, int chunk, int num_q, const DevModulus* __restri
   }
   for (int o = o_beg; o < o_end; o++) {
     int m     = o < g.skip_start ? o : o + g.skip_len;
+    if ((args.skip_mask >> m) & 1) continue;
     int prime = m < args.level ? m : num_q + (m - args.level);
     int limb  = m < args.level ? m : args.p_limb + (m - args.level);
     const DevModulus md  = mods[prime];
@@ -233,6 +234,7 @@ __global__ void __launch_bounds__(kThreads)
 moddown_combine_kernel(ModDownTail a, const Twiddle* __restrict__ p_inv,
                        const DevModulus* __restrict__ mods, uint32_t n) {
   const int     g   = blockIdx.z;
+  if ((a.skip_mask >> blockIdx.y) & 1) return;
   const u64     q   = mods[blockIdx.y].q;
   const Twiddle w   = p_inv[blockIdx.y];
   const size_t  off = (size_t)blockIdx.y * n;
@@ -254,6 +256,7 @@ template <bool TWO, bool FAST>
 __global__ void __launch_bounds__(kThreads)
 inner_product_kernel(InnerArgs a, int num_q, const DevModulus* __restrict__ mods, uint32_t n) {
   const int        m     = blockIdx.y;  // limb among level Q limbs then K P limbs
+  if ((a.skip_mask >> m) & 1) return;
   const bool       is_q  = m < a.level;
   const int        prime = is_q ? m : num_q + (m - a.level);
   const DevModulus md    = mods[prime];

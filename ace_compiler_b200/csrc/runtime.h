@@ -311,6 +311,9 @@ struct ConvGroup {
 };
 struct ConvArgs {
   int       groups, level, out_total, p_limb, in_stride, out_stride;
+  // bit m set: output m (index before the skip range is removed: Q limbs then
+  // special limbs) is not computed -- it belongs to another GPU
+  uint64_t  skip_mask = 0;
   ConvGroup g[kMaxParts];
 };
 void launch_base_conv(const ConvArgs& args);
@@ -319,6 +322,7 @@ void launch_base_conv(const ConvArgs& args);
 //   res[g][i] = (x[g][i] - t[g][i]) * P^-1 mod q_i (+ add[g][i] when add[g] is set)
 struct ModDownTail {
   int        polys, level;
+  uint64_t   skip_mask = 0;  // Q limbs left to another GPU
   u64*       res[2];
   const u64* x[2];
   const u64* t[2];
@@ -334,6 +338,7 @@ void launch_moddown_combine(const ModDownTail& args);
 // acc1/key1 may be null (single product).
 struct InnerArgs {
   int        parts, level, alpha, key_p_limb;
+  uint64_t   skip_mask;   // limbs (Q then special) left to another GPU
   const u64* in;
   const u64* ext_ptr[kMaxParts];
   const u64* key0[kMaxParts];

@@ -397,6 +397,23 @@ POLY     Swk_c0(POLY res, size_t size, bool is_rot, int32_t rot_idx);
 POLY     Swk_c1(POLY res, size_t size, bool is_rot, int32_t rot_idx);
 POLY_ARR Precomp(POLY_ARR res, size_t size, POLY input);   /* rns_poly.c:459 */
 
+/* Limb-sharded rotation for single-ciphertext latency on several GPUs (no
+ * reference counterpart: the CPU runtime has no distributed mode).  Rank r of
+ * `world` owns Q limbs [r*qb, (r+1)*qb) and special limbs [r*pb, (r+1)*pb),
+ * qb / pb from Fhert_shard_blocks; buffers use the ordinary limb-major layout
+ * with only the owned limbs valid.  The caller all-gathers gather_q (world*qb
+ * limbs) between begin and mid, and gather_p0 / gather_p1 (world*pb limbs
+ * each) between mid and end, with every rank's block in place; see
+ * ace_compiler_b200/sharded.py.  Results equal Rotate_ciph / Conjugate_ciph on
+ * the owned limbs. */
+void  Fhert_shard_blocks(size_t level, int world, int* q_block, int* p_block);
+void* Fhert_shard_begin(const int64_t* c1, size_t level, int rank, int world, int64_t* gather_q);
+void  Fhert_shard_mid(void* state, const int64_t* c1, const int64_t* gather_q, int32_t rot_idx,
+                      int is_conj, int64_t* gather_p0, int64_t* gather_p1);
+void  Fhert_shard_end(void* state, const int64_t* c0, const int64_t* gather_p0,
+                      const int64_t* gather_p1, int32_t rot_idx, int is_conj, int64_t* out0,
+                      int64_t* out1);
+
 /* Bootstrapping (ant/ckks/src/cipher.c:565-583, bootstrap.c:1549-1830): raises
  * an exhausted ciphertext back to level_after_bts levels (0 = as many as the
  * context allows) with the reference's level budget {3, 3}, cosine series and
