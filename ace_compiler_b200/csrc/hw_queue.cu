@@ -7,8 +7,8 @@
 // half-megabyte launches, so the calls are only recorded.  Every other entry
 // point of the library reaches the context through ctx(), which first replays
 // what was recorded: the recorded operations are ordered by data dependence
-// into waves, and each wave runs as one launch per operation kind covering up
-// to kHwItems limbs.
+// into waves, and each wave runs as one launch covering up to kHwItems limbs
+// (operations of different kinds share the launch).
 //
 // Dependences are tracked per limb address (operands are whole limbs, either
 // identical or disjoint).  A scratch limb that a program reuses for every
@@ -38,6 +38,7 @@ struct HwItem {
   const uint32_t* table;
   int64_t         scalar;
   uint32_t        prime;
+  uint32_t        kind;  // HwKind of this limb operation
 };
 
 struct HwLaunch {
@@ -45,28 +46,33 @@ struct HwLaunch {
   HwItem item[kHwItems];
 };
 
-template <int KIND>
+// One launch covers the limb operations of one wave, whatever their kinds: the
+// kind is uniform per block (blockIdx.y picks the item), so the switch costs no
+// divergence.
 __global__ void __launch_bounds__(kThreads)
 hw_batch_kernel(const __grid_constant__ HwLaunch launch, const DevModulus* __restrict__ mods,
                 uint32_t n) {
-  const HwItem&    it = launch.item[blockIdx.y];
-  const DevModulus m  = mods[it.prime];
-  u64              sc = 0;
-  if (KIND == HW_ADD_SCALAR || KIND == HW_MUL_SCALAR) {
+  const HwItem&    it   = launch.item[blockIdx.y];
+  const DevModulus m    = mods[it.prime];
+  const uint32_t   kind = it.kind;
+  u64              sc   = 0;
+  if (kind == HW_ADD_SCALAR || kind == HW_MUL_SCALAR) {
     int64_t s = it.scalar % (int64_t)m.q;
     sc        = s < 0 ? (u64)(s + (int64_t)m.q) : (u64)s;
   }
   for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads) {
     u64 r;
-    if (KIND == HW_ADD) r = add_mod(it.a[i], it.b[i], m.q);
-    else if (KIND == HW_SUB) r = sub_mod(it.a[i], it.b[i], m.q);
-    else if (KIND == HW_MUL) r = mul_mod(it.a[i], it.b[i], m);
-    else if (KIND == HW_MULADD) r = add_mod(it.dst[i], mul_mod(it.a[i], it.b[i], m), m.q);
-    else if (KIND == HW_ADD_SCALAR) r = add_mod(it.a[i], sc, m.q);
-    else if (KIND == HW_MUL_SCALAR) r = mul_mod(it.a[i], sc, m);
-    else if (KIND == HW_ROTATE) r = it.a[__ldg(it.table + i)];
-    else if (KIND == HW_MAC3) r = add_mod(it.c[i], mul_mod(it.a[i], it.b[i], m), m.q);
-    else r = it.a[i];
+    switch (kind) {
+      case HW_ADD: r = add_mod(it.a[i], it.b[i], m.q); break;
+      case HW_SUB: r = sub_mod(it.a[i], it.b[i], m.q); break;
+      case HW_MUL: r = mul_mod(it.a[i], it.b[i], m); break;
+      case HW_MULADD: r = add_mod(it.dst[i], mul_mod(it.a[i], it.b[i], m), m.q); break;
+      case HW_ADD_SCALAR: r = add_mod(it.a[i], sc, m.q); break;
+      case HW_MUL_SCALAR: r = mul_mod(it.a[i], sc, m); break;
+      case HW_ROTATE: r = it.a[__ldg(it.table + i)]; break;
+      case HW_MAC3: r = add_mod(it.c[i], mul_mod(it.a[i], it.b[i], m), m.q); break;
+      default: r = it.a[i]; break;
+    }
     it.dst[i] = r;
   }
 }
@@ -159,29 +165,17 @@ Slot* find_slot(HwQueue* q, const u64* addr, bool create) {
 Version& version_of(HwQueue* q, u64* addr) { return *find_slot(q, addr, true); }
 Usage&   usage_of(HwQueue* q, const u64* addr) { return *find_slot(q, addr, true); }
 
-void run_wave(Context* c, HwKind kind, const std::vector<const Node*>& wave) {
+void run_wave(Context* c, const std::vector<const Node*>& wave) {
   for (size_t off = 0; off < wave.size(); off += kHwItems) {
     HwLaunch l;
     l.count = (int)std::min<size_t>(kHwItems, wave.size() - off);
-    for (int i = 0; i < l.count; i++) l.item[i] = wave[off + i]->item;
+    for (int i = 0; i < l.count; i++) {
+      l.item[i]      = wave[off + i]->item;
+      l.item[i].kind = (uint32_t)wave[off + i]->kind;
+    }
     dim3 grid((c->N + kThreads * 2 - 1) / (kThreads * 2), l.count);
     prof_before(KID_HW_BATCH);
-#define HW_CASE(K)                                                                      \
-  case K:                                                                               \
-    hw_batch_kernel<K><<<grid, kThreads, 0, c->stream>>>(l, c->d_mod, c->N);            \
-    break;
-    switch (kind) {
-      HW_CASE(HW_ADD)
-      HW_CASE(HW_SUB)
-      HW_CASE(HW_MUL)
-      HW_CASE(HW_MULADD)
-      HW_CASE(HW_ADD_SCALAR)
-      HW_CASE(HW_MUL_SCALAR)
-      HW_CASE(HW_ROTATE)
-      HW_CASE(HW_COPY)
-      HW_CASE(HW_MAC3)
-    }
-#undef HW_CASE
+    hw_batch_kernel<<<grid, kThreads, 0, c->stream>>>(l, c->d_mod, c->N);
     prof_after(KID_HW_BATCH, l.count);
     c->launches++;
     c->hw_batched_limbs += l.count;
@@ -226,14 +220,8 @@ void hw_replay(Context* c) {
   std::vector<std::vector<const Node*>> by_level(q->max_level + 1);
   for (const Node& nd : q->nodes)
     if (!nd.dead) by_level[nd.level].push_back(&nd);
-  for (int level = 1; level <= q->max_level; level++) {
-    for (int kind = 0; kind <= (int)HW_MAC3; kind++) {
-      wave.clear();
-      for (const Node* nd : by_level[level])
-        if (nd->kind == (HwKind)kind) wave.push_back(nd);
-      if (!wave.empty()) run_wave(c, (HwKind)kind, wave);
-    }
-  }
+  for (int level = 1; level <= q->max_level; level++)
+    if (!by_level[level].empty()) run_wave(c, by_level[level]);
   // values that ended up in scratch limbs go home
   std::vector<Node> home;
   for (u64* addr : q->renamed) {
@@ -250,7 +238,7 @@ void hw_replay(Context* c) {
   if (!home.empty()) {
     wave.clear();
     for (const Node& nd : home) wave.push_back(&nd);
-    run_wave(c, HW_COPY, wave);
+    run_wave(c, wave);
   }
   for (u64* p : q->arenas) CUDA_CHECK(cudaFreeAsync(p, c->stream));
   q->arenas.clear();

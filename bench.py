@@ -442,7 +442,11 @@ def run_resnet20(args):
         roofline = {
             "bound": "hbm", "kernel": top, "achieved": round(g["gbs"], 1), "peak": peak,
             "unit": "GB/s", "frac": round(g["gbs"] / peak, 4), "peak_kind": peak_kind,
-            "traffic": None,
+            # DRAM bytes per launch: read + write per limb of the forward transform
+            # pair measured by ncu at 48 limbs (profiles/ntt_forward_48limbs_N65536.md:
+            # 25.4 MB + 77.3 MB per 48-limb launch pair), scaled by the limbs per launch
+            "traffic": (round(NTT_DRAM_BYTES_PER_LIMB * g["limbs"] / max(1, g["launches"]))
+                        if top.startswith("ntt") else None),
             "alg_bytes_per_launch": g["bytes_per_limb"] * g["limbs"] / max(1, g["launches"]),
             "avg_ms_per_launch": g["ms"] / max(1, g["launches"]),
             "share_of_image": round(g["ms"] / total_ms, 4),
@@ -502,6 +506,8 @@ def run_resnet20(args):
 # ---------------------------------------------------------------------------
 # reference arm / CPU baseline: the unmodified reference runtime on host cores
 # ---------------------------------------------------------------------------
+
+NTT_DRAM_BYTES_PER_LIMB = (25.4e6 + 77.3e6) / 48
 
 R20_SAMPLE_LEVEL = 10  # between the 19 limbs after a bootstrap and the 2 before the next
 
