@@ -933,6 +933,15 @@ void rotate_stage(Context* c, CIPHER ct, std::vector<PLAINTEXT>& plains, const F
   const int    parts = (int)std::min<size_t>((level + c->alpha - 1) / c->alpha, c->dnum);
   FHERT_ASSERT(giant <= kMaxParts, "giant step %d exceeds the fused limit", giant);
   const LimbBatch eb = ext_batch(c, level), eb2 = both_polys(eb), qb = q_only(c, level);
+  // both polynomials on the extended basis; the Q limbs of the first one also
+  // pick up the lifted c0 while they are permuted
+  LimbBatch eb2_add = eb2;
+  for (int i = 0; i < eb2_add.count; i++) {
+    LimbRef& r = eb2_add.limb[i];
+    bool     q_of_c0 = i < (int)level;
+    r.b   = q_of_c0 ? (uint16_t)i : 0;
+    r.sel = (uint8_t)((r.sel & ~2) | (q_of_c0 ? 2 : 0));  // bit 1 = "add the lifted limb"
+  }
 
   DevBuf digits(c, (size_t)parts * pw), rot(c, (size_t)giant * 2 * pw), lifted(c, 2 * pw);
   DevBuf acc(c, 2 * pw), inner(c, 2 * pw), outer(c, 2 * pw), first(c, pw), turned(c, 2 * pw);
@@ -955,8 +964,8 @@ void rotate_stage(Context* c, CIPHER ct, std::vector<PLAINTEXT>& plains, const F
     }
     uint32_t k = auto_index_for(c, val);
     digits_times_key(c, digits.p, c1, level, parts, k, acc.p);
-    launch_elementwise(EW_ADD, ptr2(acc.p), ptr2(acc.p), ptr2(lifted.p), 0, qb);
-    launch_automorphism(ptr2(dst, dst + pw), ptr2(acc.p, acc.p + pw), auto_table(c, k), eb2);
+    launch_automorphism_add(ptr2(dst, dst + pw), ptr2(acc.p, acc.p + pw), lifted.p,
+                            auto_table(c, k), eb2_add);
   }
 
   double   plain_sf     = 0;

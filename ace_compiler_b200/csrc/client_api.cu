@@ -180,21 +180,13 @@ void encode_vector(Context* c, PLAIN plain, std::vector<cplx>& values, uint32_t 
   FHERT_ASSERT(values.size() <= slots, "slot size is too small");
   FHERT_ASSERT(sf_degree >= 1, "invalid scaling factor for encode");
   const double delta = std::pow(2.0, (double)c->sf_bits);
-  values.resize(slots, cplx(0, 0));
-  embedding_inv(c, values);
-  std::vector<int64_t> msg(n, 0);
-  for (uint32_t i = 0; i < slots; i++) {
-    double  re = values[i].real() * delta + 0.5, im = values[i].imag() * delta + 0.5;
-    int64_t r = std::llround(re), m = std::llround(im);
-    msg[(size_t)i * gap]           = r < 0 ? kMax64 + r : r;
-    msg[(size_t)(i + slots) * gap] = m < 0 ? kMax64 + m : m;
-  }
   init_plain(c, plain, level, std::pow(delta, (double)sf_degree), sf_degree, slots, num_p);
   int64_t* d_msg = nullptr;
   u64*     d_pow = nullptr;
   CUDA_CHECK(cudaMallocAsync(&d_msg, n * sizeof(int64_t), c->stream));
-  CUDA_CHECK(counted_copy(d_msg, msg.data(), n * sizeof(int64_t), cudaMemcpyHostToDevice,
-                             c->stream));
+  // inverse embedding, scaling and rounding run on the device with the host
+  // routine's arithmetic (encode_gpu.cu)
+  encode_message_on_device(c, values.data(), values.size(), slots, d_msg);
   std::vector<u64> powp;
   if (sf_degree > 1) {
     // Delta^(d-1) modulo every prime (encoder.c:297-312)
@@ -209,7 +201,7 @@ void encode_vector(Context* c, PLAIN plain, std::vector<cplx>& values, uint32_t 
                                cudaMemcpyHostToDevice, c->stream));
   }
   launch_encode_split(plain->_poly._data, d_msg, d_pow, q_batch(level, num_p, c->L));
-  CUDA_CHECK(cudaStreamSynchronize(c->stream));  // msg and powp live on the host stack
+  if (d_pow) CUDA_CHECK(cudaStreamSynchronize(c->stream));  // powp lives on the host stack
   CUDA_CHECK(cudaFreeAsync(d_msg, c->stream));
   if (d_pow) CUDA_CHECK(cudaFreeAsync(d_pow, c->stream));
   plain->_poly._is_ntt = false;

@@ -523,6 +523,7 @@ void destroy_context() {
   Context* c = g_ctx;
   if (!c) return;
   hw_release(c);
+  free_encode_tables(c);
   free_bootstrap(c);
   free_keys(c);
   release_prng();

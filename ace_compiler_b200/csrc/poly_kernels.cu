@@ -88,6 +88,27 @@ automorphism_kernel(Ptr2 res, Ptr2 val, const uint32_t* __restrict__ table, Limb
     pr[i] = pv[__ldg(table + i)];
 }
 
+// res[i] = val[table[i]] (+ add[table[i]] on limbs flagged with sel bit 1, the
+// addend limb index in lr.b): the "+ P*c0" of a hoisted rotation on the
+// extended basis, folded into the gather
+__global__ void __launch_bounds__(kThreads)
+automorphism_add_kernel(Ptr2 res, Ptr2 val, const u64* __restrict__ add,
+                        const uint32_t* __restrict__ table, LimbBatch batch,
+                        const DevModulus* __restrict__ mods, uint32_t n) {
+  const LimbRef lr  = batch.limb[blockIdx.y];
+  const u64*    pv  = sel_a(val, lr, n);
+  u64*          pr  = sel_d(res, lr, n);
+  const bool    has = (lr.sel & 2) != 0;
+  const u64*    pa  = add + (size_t)lr.b * n;
+  const u64     q   = mods[lr.prime].q;
+  for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads) {
+    uint32_t t = __ldg(table + i);
+    u64      x = pv[t];
+    if (has) x = add_mod(x, pa[t], q);
+    pr[i] = x;
+  }
+}
+
 __global__ void __launch_bounds__(kThreads)
 mul_const_kernel(Ptr2 res, Ptr2 val, const Twiddle* __restrict__ consts, LimbBatch batch,
                  const DevModulus* __restrict__ mods, uint32_t n) {
@@ -378,6 +399,16 @@ void launch_automorphism(Ptr2 res, Ptr2 val, const uint32_t* table, const LimbBa
   prof_before(KID_AUTOMORPHISM);
   automorphism_kernel<<<grid_for(c->N, 2, batch.count), kThreads, 0, c->stream>>>(
       res, val, table, batch, c->N);
+  after_launch(c, KID_AUTOMORPHISM, batch.count);
+}
+
+void launch_automorphism_add(Ptr2 res, Ptr2 val, const int64_t* add, const uint32_t* table,
+                             const LimbBatch& batch) {
+  if (batch.count == 0) return;
+  Context* c = ctx();
+  prof_before(KID_AUTOMORPHISM);
+  automorphism_add_kernel<<<grid_for(c->N, 2, batch.count), kThreads, 0, c->stream>>>(
+      res, val, reinterpret_cast<const u64*>(add), table, batch, c->d_mod, c->N);
   after_launch(c, KID_AUTOMORPHISM, batch.count);
 }
 

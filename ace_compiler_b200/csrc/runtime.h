@@ -132,6 +132,8 @@ struct Context {
   // encoder tables (util/src/ntt.c:562-590): 2N-th complex roots, powers of 5
   std::vector<double>   fft_rou_re, fft_rou_im;
   std::vector<uint32_t> fft_rot_group;
+  // device copies of the encoder's roots of unity, owned by encode_gpu.cu
+  void* encode_tables = nullptr;
   // bootstrapping precomputation per slot count, owned by bootstrap.cu
   void* bootstrap = nullptr;
   // recorded per-limb vector operations awaiting replay (hw_queue.cu)
@@ -216,6 +218,13 @@ LimbBatch poly_batch(Context* c, POLY res, POLY a, POLY b, size_t level, size_t 
 LimbBatch both_polys(const LimbBatch& one);
 void      ensure_poly(POLY res, uint32_t degree, size_t num_q, size_t num_p);
 
+// ---- encode_gpu.cu ----
+// inverse embedding, scaling and rounding of `count` complex slot values (host)
+// into the message polynomial d_msg (N int64 on the device)
+void encode_message_on_device(Context* c, const std::complex<double>* values, size_t count,
+                              uint32_t slots, int64_t* d_msg);
+void free_encode_tables(Context* c);
+
 // ---- client_api.cu ----
 // encode at sf_degree and level; slots = 0 means N/2, num_p = K also fills
 // the special limbs (stored right behind the level Q limbs)
@@ -280,6 +289,10 @@ void launch_elementwise(EwOp op, Ptr2 res, Ptr2 a, Ptr2 b, int64_t scalar,
 void launch_scalars(bool mul, Ptr2 res, Ptr2 a, const u64* per_limb, const LimbBatch& batch);
 // res[dst][i] = val[a][table[i]]
 void launch_automorphism(Ptr2 res, Ptr2 val, const uint32_t* table, const LimbBatch& batch);
+// res[dst][i] = val[a][table[i]] + add[b][table[i]] on limbs whose sel has bit 1
+// set (b indexes limbs of `add`), plain gather on the others
+void launch_automorphism_add(Ptr2 res, Ptr2 val, const int64_t* add, const uint32_t* table,
+                             const LimbBatch& batch);
 // res[dst] = val[a] * consts[prime]
 void launch_mul_const(Ptr2 res, Ptr2 val, const Twiddle* consts, const LimbBatch& batch);
 // tensor product of two ciphertexts (evaluator.c:137-173), one launch:
