@@ -518,11 +518,15 @@ void mul_integer(Context* c, CIPHER res, CIPHER a, uint64_t power) {
                  ptr2(a->_c0_poly._data, a->_c1_poly._data), sc.data(), ct_batch(c, res, a));
 }
 
-// evaluator.c:260-286: multiply by x^power (power < 2N) through its transform
-void mul_monomial(Context* c, CIPHER res, CIPHER a, uint32_t power) {
-  const uint32_t n = c->N;
-  size_t   level = a->_c0_poly._num_primes;
-  uint32_t reduced = power % (2 * n), index = power % n;
+// The transform of x^power on all Q primes, built once per power and kept on
+// the device (the two powers a bootstrap uses come back at every bootstrap).
+static POLYNOMIAL* monomial_ntt(Context* c, uint32_t reduced) {
+  if (c->monomials == nullptr) c->monomials = new std::map<uint32_t, POLYNOMIAL>();
+  auto& table = *static_cast<std::map<uint32_t, POLYNOMIAL>*>(c->monomials);
+  auto  it    = table.find(reduced);
+  if (it != table.end()) return &it->second;
+  const uint32_t n = c->N, index = reduced % n;
+  const size_t   level = (size_t)c->L;
   POLYNOMIAL mono{};
   Alloc_poly_data(&mono, n, level, 0);  // zero-filled
   std::vector<int64_t> one(level);
@@ -532,13 +536,20 @@ void mul_monomial(Context* c, CIPHER res, CIPHER a, uint32_t power) {
                                cudaMemcpyHostToDevice, c->stream));
   CUDA_CHECK(cudaStreamSynchronize(c->stream));
   Conv_poly2ntt_inplace(&mono);
+  return &table.emplace(reduced, mono).first->second;
+}
+
+// evaluator.c:260-286: multiply by x^power (power < 2N) through its transform
+void mul_monomial(Context* c, CIPHER res, CIPHER a, uint32_t power) {
+  size_t      level = a->_c0_poly._num_primes;
+  POLYNOMIAL* mono  = monomial_ntt(c, power % (2 * c->N));
   shape_like(c, res, a, a->_scaling_factor, a->_sf_degree);
-  LimbBatch one_poly = poly_batch(c, &res->_c0_poly, &a->_c0_poly, &mono, level, 0);
+  // limb i of the cached transform belongs to prime i whatever the level
+  LimbBatch one_poly = poly_batch(c, &res->_c0_poly, &a->_c0_poly, mono, level, 0);
   LimbBatch both     = both_polys(one_poly);
   for (int i = one_poly.count; i < both.count; i++) both.limb[i].sel &= ~2;  // one monomial
   launch_elementwise(EW_MUL, ptr2(res->_c0_poly._data, res->_c1_poly._data),
-                     ptr2(a->_c0_poly._data, a->_c1_poly._data), ptr2(mono._data), 0, both);
-  Free_poly_data(&mono);
+                     ptr2(a->_c0_poly._data, a->_c1_poly._data), ptr2(mono->_data), 0, both);
 }
 
 // bootstrap.c:1607-1632, cipher.c:417-446: down to scaling degree 1, keep only
@@ -1187,6 +1198,12 @@ void prepare_bootstrap(Context* c, uint32_t slots) {
 }
 
 void free_bootstrap(Context* c) {
+  if (c->monomials != nullptr) {
+    auto* monos = static_cast<std::map<uint32_t, POLYNOMIAL>*>(c->monomials);
+    for (auto& kv : *monos) Free_poly_data(&kv.second);
+    delete monos;
+    c->monomials = nullptr;
+  }
   if (c->bootstrap == nullptr) return;
   auto* table = static_cast<std::map<uint32_t, Precom*>*>(c->bootstrap);
   for (auto& kv : *table) {

@@ -10,6 +10,15 @@
 // into waves, and each wave runs as one launch covering up to kHwItems limbs
 // (operations of different kinds share the launch).
 //
+// All operations but the rotation work coefficient by coefficient, so a run of
+// dependent operations on one limb ("acc += a_i * b_i" over hundreds of i) does
+// not need one wave per step: the run becomes a chain inside one wave.  A chain
+// is executed by the same blocks item after item; every thread keeps the
+// coefficients it owns, so the value it wrote for one item is the value it
+// reads for the next (it stays in a register, and is not stored at all when
+// nothing else reads it).  Only a rotation's source, which is read through a
+// permutation, has to come from an earlier wave.
+//
 // Dependences are tracked per limb address (operands are whole limbs, either
 // identical or disjoint).  A scratch limb that a program reuses for every
 // limb of a loop (the "tmp = key * digit; acc += tmp" idiom) would chain all
@@ -36,44 +45,74 @@ struct HwItem {
   const u64*      b;
   const u64*      c;
   const uint32_t* table;
-  int64_t         scalar;
+  u64             scalar;  // already reduced modulo the limb's prime
   uint32_t        prime;
-  uint32_t        kind;  // HwKind of this limb operation
+  uint32_t        kind;  // HwKind of this limb operation, kNoStore or-ed in
 };
+
+constexpr uint32_t kNoStore  = 0x100;  // the next item of the chain is the only reader
+constexpr uint32_t kKindMask = 0xff;
 
 struct HwLaunch {
-  int    count;
-  HwItem item[kHwItems];
+  int      chains;
+  uint16_t first[kHwItems + 1];  // chain y owns item[first[y] .. first[y + 1])
+  HwItem   item[kHwItems];
 };
 
-// One launch covers the limb operations of one wave, whatever their kinds: the
-// kind is uniform per block (blockIdx.y picks the item), so the switch costs no
-// divergence.
+// One launch covers one wave, whatever the kinds of its operations: blockIdx.y
+// picks a chain, whose items run one after the other on the coefficients this
+// thread owns (two per thread).  The result of an item is carried in registers
+// to the next one.
 __global__ void __launch_bounds__(kThreads)
 hw_batch_kernel(const __grid_constant__ HwLaunch launch, const DevModulus* __restrict__ mods,
                 uint32_t n) {
-  const HwItem&    it   = launch.item[blockIdx.y];
-  const DevModulus m    = mods[it.prime];
-  const uint32_t   kind = it.kind;
-  u64              sc   = 0;
-  if (kind == HW_ADD_SCALAR || kind == HW_MUL_SCALAR) {
-    int64_t s = it.scalar % (int64_t)m.q;
-    sc        = s < 0 ? (u64)(s + (int64_t)m.q) : (u64)s;
-  }
-  for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads) {
-    u64 r;
-    switch (kind) {
-      case HW_ADD: r = add_mod(it.a[i], it.b[i], m.q); break;
-      case HW_SUB: r = sub_mod(it.a[i], it.b[i], m.q); break;
-      case HW_MUL: r = mul_mod(it.a[i], it.b[i], m); break;
-      case HW_MULADD: r = add_mod(it.dst[i], mul_mod(it.a[i], it.b[i], m), m.q); break;
-      case HW_ADD_SCALAR: r = add_mod(it.a[i], sc, m.q); break;
-      case HW_MUL_SCALAR: r = mul_mod(it.a[i], sc, m); break;
-      case HW_ROTATE: r = it.a[__ldg(it.table + i)]; break;
-      case HW_MAC3: r = add_mod(it.c[i], mul_mod(it.a[i], it.b[i], m), m.q); break;
-      default: r = it.a[i]; break;
+  const uint32_t i0 = blockIdx.x * kThreads + threadIdx.x, i1 = i0 + gridDim.x * kThreads;
+  const bool     in0 = i0 < n, in1 = i1 < n;
+  const u64*     carried = nullptr;
+  u64            r0 = 0, r1 = 0;
+  auto fetch = [&](const u64* p, u64& x0, u64& x1) {
+    if (p == carried) {
+      x0 = r0;
+      x1 = r1;
+    } else {
+      x0 = in0 ? p[i0] : 0;
+      x1 = in1 ? p[i1] : 0;
     }
-    it.dst[i] = r;
+  };
+  for (int k = launch.first[blockIdx.y], end = launch.first[blockIdx.y + 1]; k < end; k++) {
+    const HwItem&    it   = launch.item[k];
+    const uint32_t   kind = it.kind & kKindMask;
+    const DevModulus m    = mods[it.prime];
+    u64              a0, a1, b0 = 0, b1 = 0, t0, t1;
+    if (kind == HW_ROTATE) {
+      a0 = in0 ? it.a[__ldg(it.table + i0)] : 0;
+      a1 = in1 ? it.a[__ldg(it.table + i1)] : 0;
+    } else {
+      fetch(it.a, a0, a1);
+    }
+    if (kind == HW_ADD || kind == HW_SUB || kind == HW_MUL || kind == HW_MAC3) fetch(it.b, b0, b1);
+    switch (kind) {
+      case HW_ADD: t0 = add_mod(a0, b0, m.q); t1 = add_mod(a1, b1, m.q); break;
+      case HW_SUB: t0 = sub_mod(a0, b0, m.q); t1 = sub_mod(a1, b1, m.q); break;
+      case HW_MUL: t0 = mul_mod(a0, b0, m); t1 = mul_mod(a1, b1, m); break;
+      case HW_MAC3: {
+        u64 c0, c1;
+        fetch(it.c, c0, c1);
+        t0 = add_mod(c0, mul_mod(a0, b0, m), m.q);
+        t1 = add_mod(c1, mul_mod(a1, b1, m), m.q);
+        break;
+      }
+      case HW_ADD_SCALAR: t0 = add_mod(a0, it.scalar, m.q); t1 = add_mod(a1, it.scalar, m.q); break;
+      case HW_MUL_SCALAR: t0 = mul_mod(a0, it.scalar, m); t1 = mul_mod(a1, it.scalar, m); break;
+      default: t0 = a0; t1 = a1; break;  // rotation (already permuted) and copy
+    }
+    r0      = t0;
+    r1      = t1;
+    carried = it.dst;
+    if (!(it.kind & kNoStore)) {
+      if (in0) it.dst[i0] = r0;
+      if (in1) it.dst[i1] = r1;
+    }
   }
 }
 
@@ -81,12 +120,15 @@ struct Node {
   HwKind kind;
   HwItem item;
   int    level;
+  int    chain;          // nodes of one chain share a wave and run in recording order
   bool   dead;
   int    src_writer[3];  // node that produced each operand, -1 = memory
   u64*   src_addr[3];    // the operands' own addresses
   int    readers;        // recorded operations that read this node's value
   bool   superseded;     // a later recorded call overwrote the same address
 };
+
+constexpr int kMixed = -2;  // read by several chains, or through a permutation
 
 // One slot per limb address seen in the current recording.  As a program
 // address it tracks the newest value of that limb (Version part); as a place
@@ -101,8 +143,10 @@ struct Slot {
   int  writer_level;
   int  readers;       // recorded operations that read it
   // Usage part
-  int read_level;
+  int read_level;     // latest wave that reads this memory, and the chain that does
+  int read_chain;     // (kMixed = more than one, or a rotation's source)
   int write_level;
+  int write_chain;
 };
 typedef Slot Version;
 typedef Slot Usage;
@@ -112,16 +156,19 @@ constexpr int kTableLog = 16;
 }  // namespace
 
 struct HwQueue {
-  std::vector<Node>                   nodes;
-  std::vector<Slot>                   table = std::vector<Slot>((size_t)1 << kTableLog);
-  uint32_t                            epoch = 1;
-  int                                 used  = 0;
-  std::vector<u64*>                   renamed;   // addresses whose value went to scratch
-  std::vector<u64*>                   arenas;
-  int                                 arena_used = kArena;
-  int                                 max_level  = 0;
-  bool                                replaying  = false;
-  bool                                eager      = false;
+  std::vector<Node>  nodes;
+  std::vector<Slot>  table = std::vector<Slot>((size_t)1 << kTableLog);
+  uint32_t           epoch = 1;
+  int                used  = 0;
+  std::vector<u64*>  renamed;   // addresses whose value went to scratch
+  std::vector<u64*>  arenas;
+  int                arena_used = kArena;
+  int                max_level  = 0;
+  std::vector<int>   chain_level;  // wave of every chain
+  bool               replaying  = false;
+  bool               eager      = false;
+  // replay scratch
+  std::vector<int>   chain_first, level_first, chain_order, flat;
 };
 
 namespace {
@@ -153,7 +200,8 @@ Slot* find_slot(HwQueue* q, const u64* addr, bool create) {
     Slot& s = q->table[h];
     if (s.epoch != q->epoch) {
       if (!create) return nullptr;
-      s = Slot{const_cast<u64*>(addr), q->epoch, const_cast<u64*>(addr), -1, 0, 0, 0, 0};
+      s = Slot{const_cast<u64*>(addr), q->epoch, const_cast<u64*>(addr), -1, 0, 0, 0, kMixed, 0,
+               kMixed};
       q->used++;
       return &s;
     }
@@ -165,23 +213,57 @@ Slot* find_slot(HwQueue* q, const u64* addr, bool create) {
 Version& version_of(HwQueue* q, u64* addr) { return *find_slot(q, addr, true); }
 Usage&   usage_of(HwQueue* q, const u64* addr) { return *find_slot(q, addr, true); }
 
-void run_wave(Context* c, const std::vector<const Node*>& wave) {
-  for (size_t off = 0; off < wave.size(); off += kHwItems) {
-    HwLaunch l;
-    l.count = (int)std::min<size_t>(kHwItems, wave.size() - off);
-    for (int i = 0; i < l.count; i++) {
-      l.item[i]      = wave[off + i]->item;
-      l.item[i].kind = (uint32_t)wave[off + i]->kind;
-    }
-    dim3 grid((c->N + kThreads * 2 - 1) / (kThreads * 2), l.count);
+// Packs chains into launches of at most kHwItems items.  A chain that does not
+// fit continues in the next launch, which the stream runs afterwards.
+struct Packer {
+  Context* c;
+  HwLaunch l;
+  int      used = 0;
+  explicit Packer(Context* ctx) : c(ctx) { l.chains = 0; }
+  void flush() {
+    if (l.chains == 0) return;
+    l.first[l.chains] = (uint16_t)used;
+    dim3 grid((c->N + kThreads * 2 - 1) / (kThreads * 2), l.chains);
     prof_before(KID_HW_BATCH);
     hw_batch_kernel<<<grid, kThreads, 0, c->stream>>>(l, c->d_mod, c->N);
-    prof_after(KID_HW_BATCH, l.count);
+    prof_after(KID_HW_BATCH, used);
     c->launches++;
-    c->hw_batched_limbs += l.count;
+    c->hw_batched_limbs += used;
     CUDA_CHECK(cudaGetLastError());
+    l.chains = 0;
+    used     = 0;
   }
-}
+  // the value of nodes[k] is needed by nobody but the next item of the piece
+  static bool only_feeds(const Node* base, const Node& nd, const Node& next) {
+    if (!nd.superseded || nd.readers == 0) return false;
+    const int self = (int)(&nd - base);
+    int       uses = 0;
+    for (int j = 0; j < 3; j++) uses += next.src_writer[j] == self;
+    return uses == nd.readers;
+  }
+  void add_chain(const Node* base, const int* member, int size) {
+    int pos = 0;
+    while (pos < size) {
+      if (used == kHwItems) flush();
+      int take = std::min(size - pos, kHwItems - used);
+      if (take < size - pos && size - pos <= kHwItems && used > 0) {
+        flush();  // fits a launch of its own: do not split it
+        continue;
+      }
+      l.first[l.chains++] = (uint16_t)used;
+      for (int i = 0; i < take; i++) {
+        const Node& nd = base[member[pos + i]];
+        HwItem&     it = l.item[used + i];
+        it             = nd.item;
+        it.kind        = (uint32_t)nd.kind;
+        if (i + 1 < take && only_feeds(base, nd, base[member[pos + i + 1]])) it.kind |= kNoStore;
+      }
+      used += take;
+      pos += take;
+      if (pos < size) flush();  // the rest of the chain has to run after this piece
+    }
+  }
+};
 
 }  // namespace
 
@@ -216,12 +298,35 @@ void hw_replay(Context* c) {
       break;
     }
   }
-  std::vector<const Node*> wave;
-  std::vector<std::vector<const Node*>> by_level(q->max_level + 1);
+  // live nodes grouped by chain (recording order inside a chain), chains by wave
+  const int chains = (int)q->chain_level.size(), nodes = (int)q->nodes.size();
+  q->chain_first.assign(chains + 1, 0);
   for (const Node& nd : q->nodes)
-    if (!nd.dead) by_level[nd.level].push_back(&nd);
-  for (int level = 1; level <= q->max_level; level++)
-    if (!by_level[level].empty()) run_wave(c, by_level[level]);
+    if (!nd.dead) q->chain_first[nd.chain + 1]++;
+  for (int i = 0; i < chains; i++) q->chain_first[i + 1] += q->chain_first[i];
+  q->flat.resize(q->chain_first[chains]);
+  {
+    std::vector<int>& fill = q->chain_order;  // borrowed as the per-chain cursor
+    fill.assign(q->chain_first.begin(), q->chain_first.end() - 1);
+    for (int i = 0; i < nodes; i++)
+      if (!q->nodes[i].dead) q->flat[fill[q->nodes[i].chain]++] = i;
+  }
+  q->level_first.assign(q->max_level + 2, 0);
+  for (int ch = 0; ch < chains; ch++) q->level_first[q->chain_level[ch] + 1]++;
+  for (int lv = 0; lv <= q->max_level; lv++) q->level_first[lv + 1] += q->level_first[lv];
+  q->chain_order.resize(chains);
+  {
+    std::vector<int> fill(q->level_first.begin(), q->level_first.end() - 1);
+    for (int ch = 0; ch < chains; ch++) q->chain_order[fill[q->chain_level[ch]]++] = ch;
+  }
+  Packer pack(c);
+  for (int lv = 1; lv <= q->max_level; lv++) {
+    for (int k = q->level_first[lv]; k < q->level_first[lv + 1]; k++) {
+      const int ch = q->chain_order[k], size = q->chain_first[ch + 1] - q->chain_first[ch];
+      if (size > 0) pack.add_chain(q->nodes.data(), q->flat.data() + q->chain_first[ch], size);
+    }
+    pack.flush();  // the next wave reads what this one wrote
+  }
   // values that ended up in scratch limbs go home
   std::vector<Node> home;
   for (u64* addr : q->renamed) {
@@ -235,16 +340,17 @@ void hw_replay(Context* c) {
     home.push_back(nd);
     sl->phys = addr;  // listed once even if renamed several times
   }
-  if (!home.empty()) {
-    wave.clear();
-    for (const Node& nd : home) wave.push_back(&nd);
-    run_wave(c, wave);
+  for (size_t i = 0; i < home.size(); i++) {
+    const int self = (int)i;
+    pack.add_chain(home.data(), &self, 1);
   }
+  pack.flush();
   for (u64* p : q->arenas) CUDA_CHECK(cudaFreeAsync(p, c->stream));
   q->arenas.clear();
   q->arena_used = kArena;
   q->nodes.clear();
   q->renamed.clear();
+  q->chain_level.clear();
   q->epoch++;
   q->used = 0;
   q->max_level = 0;
@@ -270,12 +376,32 @@ bool hw_record(Context* c, HwKind kind, int64_t* res, const int64_t* a, const in
                  kind <= HW_MULADD ? reinterpret_cast<u64*>(const_cast<int64_t*>(b)) : nullptr,
                  kind == HW_MULADD ? dst : nullptr};
   Node nd{};
-  nd.kind        = kind;
+  nd.kind        = kind == HW_MULADD ? HW_MAC3 : kind;
   nd.item.table  = table;
-  nd.item.scalar = scalar;
   nd.item.prime  = (uint32_t)prime;
   nd.dead        = false;
-  int  level     = 0;
+  if (kind == HW_ADD_SCALAR || kind == HW_MUL_SCALAR) {
+    const int64_t qv = (int64_t)c->primes[prime], sv = scalar % qv;
+    nd.item.scalar   = (u64)(sv < 0 ? sv + qv : sv);
+  }
+  // What this operation has to wait for.  `hard`: the latest wave that must be
+  // complete before it starts.  soft: waves it may share, provided it runs in
+  // the same chain after the operation it depends on (same coefficient, same
+  // thread).
+  int hard = 0, soft_level = 0, soft_chain = -1;
+  bool soft_clash = false;
+  auto depend = [&](int level, int chain, bool permuted) {
+    if (level <= 0) return;
+    if (permuted || chain < 0) {
+      hard = std::max(hard, level);
+    } else if (level > soft_level) {
+      soft_level = level;
+      soft_chain = chain;
+      soft_clash = false;
+    } else if (level == soft_level && chain != soft_chain) {
+      soft_clash = true;
+    }
+  };
   bool in_place  = false;
   const u64* phys[3] = {nullptr, nullptr, nullptr};
   Slot*      seen[3] = {nullptr, nullptr, nullptr};
@@ -286,13 +412,13 @@ bool hw_record(Context* c, HwKind kind, int64_t* res, const int64_t* a, const in
     Version& v = version_of(q, src[i]);
     seen[i]    = &v;
     phys[i]    = v.phys;
-    level      = std::max(level, v.writer_level);
+    depend(v.writer_level, v.writer >= 0 ? q->nodes[v.writer].chain : kMixed,
+           kind == HW_ROTATE && i == 0);
     nd.src_writer[i] = v.writer;
     if (src[i] == dst) in_place = true;
   }
   nd.readers    = 0;
   nd.superseded = false;
-  level += 1;
   Version& dv = version_of(q, dst);
   u64*     out;
   if (dv.writer >= 0) q->nodes[dv.writer].superseded = true;
@@ -302,21 +428,42 @@ bool hw_record(Context* c, HwKind kind, int64_t* res, const int64_t* a, const in
     out = dv.phys;
     if (!in_place && dv.readers == 0 && dv.writer >= 0) q->nodes[dv.writer].dead = true;
     Usage& u = out == dst ? dv : usage_of(q, out);
-    level    = std::max(level, std::max(u.read_level, u.write_level) + 1);
+    depend(u.read_level, u.read_chain, false);
+    depend(u.write_level, u.write_chain, false);
+  }
+  int level = std::max(hard + 1, soft_level), chain;
+  if (soft_level == level && !soft_clash) {
+    chain = soft_chain;  // continues the chain of what it depends on
+  } else {
+    if (soft_level == level) level++;  // depends on two chains of that wave
+    chain = (int)q->chain_level.size();
+    q->chain_level.push_back(level);
   }
   for (int i = 0; i < 3; i++) {
     if (src[i] == nullptr) continue;
     Version& v = *seen[i];
     v.readers++;
     if (v.writer >= 0) q->nodes[v.writer].readers++;
-    Usage& u     = v.phys == v.key ? v : usage_of(q, v.phys);
-    u.read_level = std::max(u.read_level, level);
+    Usage&     u        = v.phys == v.key ? v : usage_of(q, v.phys);
+    const bool permuted = kind == HW_ROTATE && i == 0;
+    if (level > u.read_level) {
+      u.read_level = level;
+      u.read_chain = permuted ? kMixed : chain;
+    } else if (level == u.read_level && (permuted || u.read_chain != chain)) {
+      u.read_chain = kMixed;
+    }
   }
   nd.item.dst = out;
   nd.item.a   = phys[0];
   nd.item.b   = phys[1];
+  nd.item.c   = phys[2];
   nd.level    = level;
-  (out == dst ? dv : usage_of(q, out)).write_level = level;
+  nd.chain    = chain;
+  {
+    Usage& u      = out == dst ? dv : usage_of(q, out);
+    u.write_level = level;
+    u.write_chain = chain;
+  }
   if (out != dst) q->renamed.push_back(dst);
   Version& fresh    = dv;
   fresh.phys        = out;

@@ -134,6 +134,8 @@ struct Context {
   std::vector<uint32_t> fft_rot_group;
   // device copies of the encoder's roots of unity, owned by encode_gpu.cu
   void* encode_tables = nullptr;
+  // transforms of the monomials the bootstrap multiplies by, owned by bootstrap.cu
+  void* monomials = nullptr;
   // bootstrapping precomputation per slot count, owned by bootstrap.cu
   void* bootstrap = nullptr;
   // recorded per-limb vector operations awaiting replay (hw_queue.cu)

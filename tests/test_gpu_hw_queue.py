@@ -100,6 +100,61 @@ def test_random_limb_programs(gpu, seed):
     assert launches < 400  # recorded calls were merged into fewer launches
 
 
+@pytest.mark.parametrize("seed", range(20, 26))
+def test_random_limb_programs_on_few_limbs(gpu, seed):
+    """Four limbs only: nearly every call depends on the one before it, through
+    values, overwritten sources and rotated sources alike."""
+    got, want = run_program(gpu, seed, 500, limbs=4)
+    assert np.array_equal(got, want)
+
+
+def test_long_accumulation_runs_as_one_chain(gpu):
+    """acc[l] += w[i][l] * rot_i(x)[l] over 150 terms with one shared product limb
+    and one shared rotated limb per l: the sums of one limb form one chain, which
+    here is longer than a launch holds and continues in the next one."""
+    lib = gpu.lib
+    rng = np.random.default_rng(5)
+    limbs, terms = 3, 300
+    primes = gpu.primes[:limbs]
+    order_dev = lib.Auto_order(1)
+    ident = gpu.new_poly(2)
+    gpu.upload(ident, np.stack([np.arange(N, dtype=np.int64), np.zeros(N, np.int64)]))
+    lib.Hw_rotate(gpu.limb_ptr(ident, 1), gpu.limb_ptr(ident, 0), order_dev, gpu.modulus(0), N)
+    table = gpu.download(ident)[1].astype(np.int64)
+    gpu.free(ident)
+    hx = np.stack([rng.integers(0, p, (terms, N), dtype=np.int64) for p in primes])  # [l][i]
+    hw = np.stack([rng.integers(0, p, (terms, N), dtype=np.int64) for p in primes])
+    # operand i of limb l lives in limb i % L of the (i // L)-th polynomial of its pool
+    pools = {}
+    for name, host in (("x", hx), ("w", hw)):
+        for l in range(limbs):
+            pools[name, l] = [gpu.new_poly(L, data=host[l][k:k + L]) for k in range(0, terms, L)]
+
+    def operand(name, l, i):
+        return gpu.limb_ptr(pools[name, l][i // L], i % L)
+
+    acc = gpu.new_poly(limbs); gpu.upload(acc, np.zeros((limbs, N), np.int64))
+    rot = gpu.new_poly(1); tmp = gpu.new_poly(1)
+    lib.Fhert_sync()
+    before = lib.Fhert_kernel_launches()
+    for i in range(terms):
+        for l in range(limbs):
+            m = gpu.modulus(l)
+            lib.Hw_rotate(gpu.limb_ptr(rot, 0), operand("x", l, i), order_dev, m, N)
+            lib.Hw_modmul(gpu.limb_ptr(tmp, 0), operand("w", l, i), gpu.limb_ptr(rot, 0), m, N)
+            lib.Hw_modadd(gpu.limb_ptr(acc, l), gpu.limb_ptr(acc, l), gpu.limb_ptr(tmp, 0), m, N)
+    lib.Fhert_sync()
+    launches = lib.Fhert_kernel_launches() - before
+    assert launches <= 20, launches
+    want = np.zeros((limbs, N), dtype=object)
+    for l in range(limbs):
+        for i in range(terms):
+            want[l] = (want[l] + hw[l][i].astype(object) * hx[l][i][table].astype(object)) % primes[l]
+    assert np.array_equal(gpu.download(acc), want.astype(np.int64))
+    for p in [q for pool in pools.values() for q in pool] + [acc, rot, tmp]:
+        gpu.free(p)
+
+
 def test_key_switch_idiom_is_merged(gpu):
     """tmp = key * digit; acc += tmp for every limb with one shared tmp: two
     launches, not two per limb."""
