@@ -165,8 +165,8 @@ void Finalize_context(void) {
 uint32_t Degree(void) { return ctx_noflush()->N; }
 size_t   Get_q_cnt(void) { return ctx_noflush()->L; }
 size_t   Get_p_cnt(void) { return ctx_noflush()->K; }
-size_t   Get_q_parts(void) { return ctx()->dnum; }
-size_t   Get_part_size(void) { return ctx()->alpha; }
+size_t   Get_q_parts(void) { return ctx_noflush()->dnum; }
+size_t   Get_part_size(void) { return ctx_noflush()->alpha; }
 MODULUS* Q_modulus(void) { return ctx_noflush()->moduli.data(); }
 MODULUS* P_modulus(void) { return ctx_noflush()->moduli.data() + ctx_noflush()->L; }
 double   Get_default_sc(void) { return std::pow(2.0, (double)ctx_noflush()->sf_bits); }
@@ -510,7 +510,7 @@ POLY Rescale(POLY res, POLY poly) {
 
 size_t Num_decomp(POLY poly) {
   // crt.c:1135: ceil(level / alpha), capped by dnum
-  Context* c = ctx();
+  Context* c = ctx_noflush();
   size_t   d = (poly->_num_primes + c->alpha - 1) / c->alpha;
   return d > (size_t)c->dnum ? (size_t)c->dnum : d;
 }
@@ -603,14 +603,59 @@ void fhert_raise_parts(Context* c, const int64_t* src, bool is_ntt, size_t level
   if (is_ntt) fhert_launch_ntt_chunked(ptr2(ext_base), ptr2(ext_base), out_limbs, false);
 }
 
+// Hands digit `part` of the raised polynomial kept in c->raised to res: every
+// limb of res becomes an alias of the kept copy in the recorder, so the
+// per-limb calls recorded around it need no launch in between.
+static bool modup_serve(Context* c, POLY res, POLY poly, uint32_t part) {
+  auto& m = c->raised;
+  if (!m.valid || m.src != poly->_data || m.level != poly->_num_primes ||
+      m.is_ntt != poly->_is_ntt || (int)part >= m.parts)
+    return false;
+  const size_t   n = c->N, ext_limbs = m.level + c->K;
+  const int64_t* digit = m.digits + (size_t)part * ext_limbs * n;
+  for (size_t i = 0; i < ext_limbs; i++) {
+    size_t limb = i < m.level ? i : p_offset(res) + (i - m.level);
+    if (!hw_alias(c, res->_data + limb * n, digit + i * n)) return false;
+  }
+  res->_is_ntt = poly->_is_ntt;
+  return true;
+}
+
 POLY Decomp_modup(POLY res, POLY poly, uint32_t part) {
-  Context* c     = ctx();
+  Context* c     = ctx_noflush();
   size_t   level = poly->_num_primes;
   FHERT_ASSERT(res->_data && res->_num_primes == level && res->_num_primes_p == (size_t)c->K,
                "Decomp_modup: result must hold level + K limbs");
   size_t start = (size_t)c->alpha * part;
   FHERT_ASSERT(start < level, "Decomp_modup: digit out of range");
-  size_t len = std::min((size_t)c->alpha, level - start);
+  if (modup_serve(c, res, poly, part)) return res;
+  c = ctx();  // deferred work first; this also drops digits kept for another polynomial
+  size_t len   = std::min((size_t)c->alpha, level - start);
+  int    parts = (int)((level + c->alpha - 1) / c->alpha);
+  // A program raises the digits of one polynomial one after the other
+  // (hal: the emitted key-switch loop), so the first call raises all of them
+  // in one batch of launches and the following calls only hand them out.
+  if (part == 0 && parts > 1 && !c->draining && hw_recording(c)) {
+    const size_t n = c->N, ext_limbs = level + c->K;
+    int64_t*     digits = nullptr;
+    CUDA_CHECK(cudaMallocAsync(&digits, (size_t)parts * ext_limbs * n * sizeof(int64_t), c->stream));
+    fhert_raise_parts(c, poly->_data, poly->_is_ntt, level, 0, parts, digits, ext_limbs, (int)level);
+    for (int p = 0; p < parts; p++) {  // each digit's own limbs are the polynomial's
+      size_t first = (size_t)c->alpha * p, cnt = std::min((size_t)c->alpha, level - first);
+      CUDA_CHECK(counted_copy(digits + ((size_t)p * ext_limbs + first) * n, poly->_data + first * n,
+                                 cnt * n * sizeof(int64_t), cudaMemcpyDeviceToDevice, c->stream));
+    }
+    hw_free_after_replay(c, digits);
+    c->raised.valid  = true;
+    c->raised.src    = poly->_data;
+    c->raised.level  = level;
+    c->raised.is_ntt = poly->_is_ntt;
+    c->raised.parts  = parts;
+    c->raised.digits = digits;
+    bool served = modup_serve(c, res, poly, 0);
+    FHERT_ASSERT(served, "Decomp_modup: kept digits not usable");
+    return res;
+  }
   fhert_raise_parts(c, poly->_data, poly->_is_ntt, level, (int)part, (int)part + 1, res->_data, 0,
               (int)p_offset(res));
   CUDA_CHECK(counted_copy(res->_data + start * c->N, poly->_data + start * c->N,
@@ -770,7 +815,7 @@ POLY Automorphism_transform(POLY res, POLY poly, int64_t* order) {
 uint32_t Auto_idx(int32_t rot_idx) { return auto_index_for(ctx(), rot_idx); }
 
 int64_t* Auto_order(int32_t rot_idx) {
-  Context* c = ctx();
+  Context* c = ctx_noflush();  // a table of the library's own: touches no program data
   uint32_t k = (rot_idx == (int32_t)(2 * c->N - 1)) ? (uint32_t)rot_idx : auto_index_for(c, rot_idx);
   return reinterpret_cast<int64_t*>(auto_table(c, k));
 }
@@ -782,7 +827,7 @@ static uint32_t key_id_for(Context* c, bool is_rot, int32_t rot_idx) {
 }
 
 SW_KEY Swk(bool is_rot, int32_t rot_idx) {
-  Context*    c = ctx();
+  Context*    c = ctx_noflush();  // looks a key up: touches no program data
   SWITCH_KEY* k = key_slot(c, key_id_for(c, is_rot, rot_idx), false);
   FHERT_ASSERT(k != nullptr, "cannot find %s key for index %d", is_rot ? "rotation" : "relin",
                rot_idx);

@@ -142,6 +142,7 @@ struct Slot {
   int  writer;        // node that produces it, -1 = already in memory
   int  writer_level;
   int  readers;       // recorded operations that read it
+  bool written;       // some recorded operation wrote this address (sticky)
   // Usage part
   int read_level;     // latest wave that reads this memory, and the chain that does
   int read_chain;     // (kMixed = more than one, or a rotation's source)
@@ -162,6 +163,7 @@ struct HwQueue {
   int                used  = 0;
   std::vector<u64*>  renamed;   // addresses whose value went to scratch
   std::vector<u64*>  arenas;
+  std::vector<void*> borrowed;  // device memory to release after the next replay
   int                arena_used = kArena;
   int                max_level  = 0;
   std::vector<int>   chain_level;  // wave of every chain
@@ -200,8 +202,8 @@ Slot* find_slot(HwQueue* q, const u64* addr, bool create) {
     Slot& s = q->table[h];
     if (s.epoch != q->epoch) {
       if (!create) return nullptr;
-      s = Slot{const_cast<u64*>(addr), q->epoch, const_cast<u64*>(addr), -1, 0, 0, 0, kMixed, 0,
-               kMixed};
+      s = Slot{const_cast<u64*>(addr), q->epoch, const_cast<u64*>(addr), -1, 0, 0, false, 0,
+               kMixed, 0, kMixed};
       q->used++;
       return &s;
     }
@@ -269,7 +271,8 @@ struct Packer {
 
 void hw_replay(Context* c) {
   HwQueue* q = c->hw_queue;
-  if (q == nullptr || q->nodes.empty() || q->replaying) return;
+  if (q == nullptr || q->replaying) return;
+  if (q->nodes.empty() && q->renamed.empty() && q->borrowed.empty()) return;
   q->replaying = true;
   // "tmp = a * b; d = x + tmp" with tmp read once, a and b untouched by the
   // recording: one multiply-add; a product overwritten later in the same
@@ -277,7 +280,7 @@ void hw_replay(Context* c) {
   auto untouched = [&](const Node& p, int t) {
     if (p.src_writer[t] != -1) return false;
     Slot* sl = find_slot(q, p.src_addr[t], false);
-    return sl == nullptr || sl->writer == -1;
+    return sl == nullptr || !sl->written;
   };
   for (Node& sum : q->nodes) {
     if (sum.dead || sum.kind != HW_ADD) continue;
@@ -347,6 +350,9 @@ void hw_replay(Context* c) {
   pack.flush();
   for (u64* p : q->arenas) CUDA_CHECK(cudaFreeAsync(p, c->stream));
   q->arenas.clear();
+  for (void* p : q->borrowed) CUDA_CHECK(cudaFreeAsync(p, c->stream));
+  q->borrowed.clear();
+  c->raised.valid = false;  // its digits were among the borrowed memory
   q->arena_used = kArena;
   q->nodes.clear();
   q->renamed.clear();
@@ -363,6 +369,32 @@ void hw_release(Context* c) {
   hw_replay(c);
   delete c->hw_queue;
   c->hw_queue = nullptr;
+}
+
+bool hw_alias(Context* c, int64_t* dst_, const int64_t* src_) {
+  HwQueue* q = queue_of(c);
+  if (q->eager) return false;
+  u64*     dst = reinterpret_cast<u64*>(dst_);
+  Version& dv  = version_of(q, dst);
+  if (dv.writer >= 0) {
+    q->nodes[dv.writer].superseded = true;
+    if (dv.readers == 0) q->nodes[dv.writer].dead = true;  // overwritten unread
+  }
+  dv.phys         = reinterpret_cast<u64*>(const_cast<int64_t*>(src_));
+  dv.writer       = -1;
+  dv.writer_level = 0;
+  dv.readers      = 0;
+  dv.written      = true;
+  q->renamed.push_back(dst);  // the value goes to its real address at the end of the replay
+  c->hw_pending = true;
+  return true;
+}
+
+bool hw_recording(Context* c) { return !queue_of(c)->eager; }
+
+void hw_free_after_replay(Context* c, void* device_memory) {
+  queue_of(c)->borrowed.push_back(device_memory);
+  c->hw_pending = true;
 }
 
 // Records res = a (kind) b.  Returns false when recording is switched off
@@ -421,6 +453,9 @@ bool hw_record(Context* c, HwKind kind, int64_t* res, const int64_t* a, const in
   nd.superseded = false;
   Version& dv = version_of(q, dst);
   u64*     out;
+  dv.written = true;
+  if (c->raised.valid && res >= c->raised.src && res < c->raised.src + c->raised.level * c->N)
+    c->raised.valid = false;  // the polynomial being raised changes: later digits start afresh
   if (dv.writer >= 0) q->nodes[dv.writer].superseded = true;
   if (!in_place && dv.readers > 0) {
     out = scratch_limb(c, q);  // earlier readers keep the old value

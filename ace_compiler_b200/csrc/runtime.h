@@ -153,6 +153,17 @@ struct Context {
     int            p_limb = 0;
     bool           is_ntt = true;
   } pair_wait;
+  // All digits of the polynomial a program is raising, made at its first
+  // Decomp_modup call and handed out by the following ones (api.cu).  The
+  // storage belongs to the recorder and is released by the next replay.
+  struct {
+    bool           valid = false;
+    const int64_t* src   = nullptr;  // the polynomial's limbs
+    size_t         level = 0;
+    bool           is_ntt = true;
+    int            parts = 0;
+    int64_t*       digits = nullptr;  // [parts][level + K] limbs
+  } raised;
   // bytes moved between host and device since the context was made
   uint64_t h2d_bytes = 0, d2h_bytes = 0;
 
@@ -245,6 +256,11 @@ enum HwKind : uint8_t {
 // records res = a (kind) b on one limb; false = recording is off, launch now
 bool hw_record(Context* c, HwKind kind, int64_t* res, const int64_t* a, const int64_t* b,
                const uint32_t* table, int64_t scalar, int prime);
+// the newest value of limb dst is the contents of src, private memory that no
+// one else writes and that lives until the next replay; false = recording is off
+bool hw_alias(Context* c, int64_t* dst, const int64_t* src);
+void hw_free_after_replay(Context* c, void* device_memory);
+bool hw_recording(Context* c);  // false under FHERT_EAGER_HW=1
 void hw_replay(Context* c);   // run everything recorded so far
 void pair_flush(Context* c);  // run a waiting Mod_down / Rescale on its own (api.cu)
 void hw_release(Context* c);

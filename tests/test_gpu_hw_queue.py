@@ -205,3 +205,84 @@ def test_waiting_rescale_runs_before_younger_limb_calls(gpu):
     assert np.array_equal(gpu.download(acc), want)
     for p in (src, ref_out, out, acc):
         gpu.free(p)
+
+
+def _raise_all(gpu, src, level, order):
+    """Decomp_modup of every digit in the given order, each into its own result."""
+    lib = gpu.lib
+    parts = int(lib.Num_decomp(src))
+    out = {}
+    for p in order:
+        ext = gpu.new_poly(level, extended=True)
+        lib.Decomp_modup(ext, src, p)
+        out[p] = ext
+    assert sorted(out) == list(range(parts))
+    return out
+
+
+def test_digits_raised_together_equal_digits_raised_alone(gpu):
+    """Digit 0 first makes the library raise all digits at once and hand the others
+    out later; any other order raises each digit on its own.  Same residues."""
+    lib = gpu.lib
+    rng = np.random.default_rng(41)
+    level = L
+    data = np.stack([rng.integers(0, p, N, dtype=np.int64) for p in gpu.primes[:level]])
+    src = gpu.new_poly(level, data=data)
+    parts = int(lib.Num_decomp(src))
+    assert parts >= 2
+    alone = _raise_all(gpu, src, level, list(range(1, parts)) + [0])
+    want = {p: gpu.download(alone[p]) for p in alone}
+    lib.Fhert_sync()
+    before = lib.Fhert_kernel_launches()
+    together = _raise_all(gpu, src, level, list(range(parts)))
+    launches = lib.Fhert_kernel_launches() - before
+    for p in range(parts):
+        assert np.array_equal(gpu.download(together[p]), want[p]), p
+    assert launches <= 8, launches  # one batch of launches, not one per digit
+    for p in list(alone.values()) + list(together.values()) + [src]:
+        gpu.free(p)
+
+
+def test_kept_digits_follow_the_program(gpu):
+    """One result polynomial reused for every digit with per-limb calls in between
+    (the emitted key-switch loop); then the source changes between two digits, and
+    the later digit must come from the changed source."""
+    lib = gpu.lib
+    rng = np.random.default_rng(43)
+    level = L
+    primes = gpu.primes
+    data = np.stack([rng.integers(0, p, N, dtype=np.int64) for p in primes[:level]])
+    src = gpu.new_poly(level, data=data)
+    parts = int(lib.Num_decomp(src))
+    alone = _raise_all(gpu, src, level, list(range(1, parts)) + [0])
+    want = {p: gpu.download(alone[p]) for p in alone}
+    # acc_i = sum over digits of ext_i (Q limbs only), ext shared by all digits
+    ext = gpu.new_poly(level, extended=True)
+    acc = gpu.new_poly(level)
+    gpu.upload(acc, np.zeros((level, N), np.int64))
+    for p in range(parts):
+        lib.Decomp_modup(ext, src, p)
+        for i in range(level):
+            lib.Hw_modadd(gpu.limb_ptr(acc, i), gpu.limb_ptr(acc, i), gpu.limb_ptr(ext, i),
+                          gpu.modulus(i), N)
+    total = np.zeros((level, N), dtype=object)
+    for p in range(parts):
+        total += want[p][:level].astype(object)
+    for i in range(level):
+        total[i] %= primes[i]
+    assert np.array_equal(gpu.download(acc), total.astype(np.int64))
+    assert np.array_equal(gpu.download(ext), want[parts - 1])  # the last digit stays in ext
+    # the source changes after digit 0 was handed out
+    lib.Decomp_modup(ext, src, 0)
+    lib.Hw_modadd_scalar(gpu.limb_ptr(src, level - 1), gpu.limb_ptr(src, level - 1), 5,
+                         gpu.modulus(level - 1), N)
+    lib.Decomp_modup(ext, src, parts - 1)
+    got = gpu.download(ext)
+    changed = data.copy()
+    changed[level - 1] = (changed[level - 1] + 5) % primes[level - 1]
+    src2 = gpu.new_poly(level, data=changed)
+    ref = gpu.new_poly(level, extended=True)
+    lib.Decomp_modup(ref, src2, parts - 1)
+    assert np.array_equal(got, gpu.download(ref))
+    for p in list(alone.values()) + [src, src2, ext, acc, ref]:
+        gpu.free(p)
