@@ -58,6 +58,7 @@ using CacheKey = std::tuple<uint32_t, size_t, size_t, uint32_t, uint32_t>;
 struct CacheState {
   std::map<CacheKey, PLAINTEXT> entries;
   std::set<const void*>         owned;  // limb storage held by the cache
+  bool                          bypass = false;  // encode every request, keep the cache as it is
   size_t                        bytes = 0, budget = 0, hits = 0, misses = 0;
 };
 CacheState g_cache;
@@ -81,7 +82,11 @@ void* plain_from_entry(void* pt, uint32_t index, size_t ofst, size_t len, uint32
                        uint32_t level) {
   PLAIN        plain = (PLAIN)pt;
   const float* data  = entry_floats(index, ofst, len);
-  if (g_cache.budget == 0) {
+  if (g_cache.budget == 0 || g_cache.bypass) {
+    if (plain->_poly._data && cache_owns(plain->_poly._data)) {  // a borrowed view: drop it
+      plain->_poly._data             = nullptr;
+      plain->_poly._num_alloc_primes = 0;
+    }
     Encode_float(plain, const_cast<float*>(data), len, scale, level);
     return pt;
   }
@@ -153,6 +158,8 @@ void Pt_mgr_fini(void) {
   g_cache = CacheState();
   g_file  = DataFile();
 }
+
+void Fhert_pt_cache_bypass(int on) { g_cache.bypass = on != 0; }
 
 void Fhert_pt_cache_stats(size_t* entries, size_t* bytes, size_t* hits, size_t* misses) {
   if (entries) *entries = g_cache.entries.size();

@@ -469,6 +469,9 @@ void* Pt_from_msg_ofst(void* pt, uint32_t index, size_t ofst, size_t len, uint32
                        uint32_t level);
 void  Free_data(void* poly);
 void  Fhert_pt_cache_stats(size_t* entries, size_t* bytes, size_t* hits, size_t* misses);
+/* on != 0: every Pt_from_msg encodes afresh (as the CPU runtime does) while the cache keeps
+ * what it holds; for measuring a program with and without resident weight plaintexts. */
+void  Fhert_pt_cache_bypass(int on);
 
 /* Checks emitted by the compiler's run-time validation mode
  * (include/common/rt_validate.h:20-49, common/src/rt_validate.c:16-57) */

@@ -80,6 +80,22 @@ def test_plaintexts_from_data_file(setup, cache_mb):
         entries, _, hits, misses = [s.value for s in stats]
         if cache_mb:
             assert (entries, hits, misses) == (len(CASES), len(CASES), len(CASES))
+            # bypass: encoded afresh (the plaintext owns its limbs), the cache untouched
+            gpu.lib.Fhert_pt_cache_bypass(1)
+            index, ofst, length, scale, level = CASES[1]
+            pt = rt.PLAINTEXT()
+            gpu.lib.Pt_from_msg(C.byref(pt), index, length, scale, level)   # cached view first
+            gpu.lib.Fhert_pt_cache_bypass(0)
+            gpu.lib.Pt_from_msg(C.byref(pt), index, length, scale, level)
+            gpu.lib.Fhert_pt_cache_bypass(1)
+            gpu.lib.Pt_from_msg(C.byref(pt), index, length, scale, level)   # replaces the view
+            want = ref_plain(ref, rt, index, ofst, length, scale, level)[0]
+            assert np.array_equal(gpu.download(C.pointer(pt._poly)), want)
+            gpu.lib.Free_data(C.byref(pt._poly))
+            gpu.lib.Fhert_pt_cache_bypass(0)
+            gpu.lib.Fhert_pt_cache_stats(*[C.byref(s) for s in stats])
+            assert [s.value for s in stats][0] == len(CASES)
+            assert [s.value for s in stats][2] == len(CASES) + 1
         else:
             assert (entries, hits) == (0, 0)
     finally:
