@@ -35,7 +35,7 @@ namespace fhert {
 namespace {
 
 constexpr int kThreads  = 256;
-constexpr int kHwItems  = 256;   // limbs per launch
+constexpr int kHwItems  = 384;   // limb operations per launch (21 KiB of kernel parameters)
 constexpr int kArena    = 64;    // scratch limbs per allocation
 constexpr int kMaxNodes = 8192;  // replay at the latest after this many calls
 
@@ -383,8 +383,7 @@ bool hw_alias(Context* c, int64_t* dst_, const int64_t* src_) {
   dv.phys         = reinterpret_cast<u64*>(const_cast<int64_t*>(src_));
   dv.writer       = -1;
   dv.writer_level = 0;
-  dv.readers      = 0;
-  dv.written      = true;
+  dv.readers      = 0;  // `written` stays: only recorded operations count as writes
   q->renamed.push_back(dst);  // the value goes to its real address at the end of the replay
   c->hw_pending = true;
   return true;

@@ -30,7 +30,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", default="ntt",
                     choices=["ntt", "intt", "modmul", "automorphism", "rescale", "modup",
-                             "moddown", "rotate", "hmult"])
+                             "moddown", "rotate", "hmult", "keyloop"])
     ap.add_argument("--degree", type=int, default=65536)
     ap.add_argument("--levels", type=int, default=36, help="L of the context and of the operands")
     ap.add_argument("--dnum", type=int, default=3)
@@ -47,7 +47,7 @@ def main():
     rng = np.random.default_rng(7)
     ext_primes = gpu.primes
 
-    if args.op in ("rotate", "hmult"):
+    if args.op in ("rotate", "hmult", "keyloop"):
         for is_rot, idx in ((False, 0), (True, 1)):
             for part in range(gpu.dnum):
                 for which in (0, 1):
@@ -58,7 +58,7 @@ def main():
         if args.op in ("ntt", "intt", "moddown"):
             polys.append(gpu.new_poly(L, extended=True, data=uniform(rng, ext_primes, n),
                                       is_ntt=(args.op != "ntt")))
-        elif args.op in ("rotate", "hmult"):
+        elif args.op in ("rotate", "hmult", "keyloop"):
             ciphs.append(gpu.new_ciph(uniform(rng, gpu.primes[:L], n),
                                       uniform(rng, gpu.primes[:L], n)))
         else:
@@ -66,7 +66,38 @@ def main():
     out = gpu.new_poly(L, extended=(args.op == "modup"))
     out_ct, prod = rt.CIPHERTEXT(), rt.CIPHERTEXT()
 
+    if args.op == "keyloop":
+        # the key-switch loop a compiled program emits: per digit Decomp_modup, then per
+        # limb tmp = key * digit; acc += tmp for both key polynomials, then two Mod_down
+        ext = gpu.new_poly(L, extended=True)
+        acc = [gpu.new_poly(L, extended=True) for _ in range(2)]
+        down = [gpu.new_poly(L) for _ in range(2)]
+        tmp = gpu.new_poly(1)
+        swk = lib.Swk(True, 1)
+        zeros = np.zeros((L + K, n), np.int64)
+
+    def key_loop(i):
+        c1 = C.pointer(ciphs[i % len(ciphs)]._c1_poly)
+        for a in acc:
+            gpu.upload(a, zeros)
+        for part in range(int(lib.Num_decomp(c1))):
+            lib.Decomp_modup(ext, c1, part)
+            keys = (lib.Pk0_at(swk, part), lib.Pk1_at(swk, part))
+            for limb in range(L + K):
+                m = gpu.modulus(limb)  # operands are at the top level: limb i is prime i
+                for key, a in zip(keys, acc):
+                    lib.Hw_modmul(gpu.limb_ptr(tmp, 0), gpu.limb_ptr(key, limb),
+                                  gpu.limb_ptr(ext, limb), m, n)
+                    lib.Hw_modadd(gpu.limb_ptr(a, limb), gpu.limb_ptr(a, limb),
+                                  gpu.limb_ptr(tmp, 0), m, n)
+        for d, a in zip(down, acc):
+            lib.Mod_down(d, a)
+        lib.Fhert_sync()
+        return (3 * L + 2 * beta * (L + K)) * W
+
     def run(i):
+        if args.op == "keyloop":
+            return key_loop(i)
         if args.op == "ntt":
             p = polys[i % len(polys)]
             p.contents._is_ntt = False
