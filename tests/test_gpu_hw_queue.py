@@ -109,12 +109,12 @@ def test_random_limb_programs_on_few_limbs(gpu, seed):
 
 
 def test_long_accumulation_runs_as_one_chain(gpu):
-    """acc[l] += w[i][l] * rot_i(x)[l] over 450 terms with one shared product limb
+    """acc[l] += w[i][l] * rot_i(x)[l] over 448 terms with one shared product limb
     and one shared rotated limb per l: the sums of one limb form one chain, which
     here is longer than a launch holds and continues in the next one."""
     lib = gpu.lib
     rng = np.random.default_rng(5)
-    limbs, terms = 3, 450
+    limbs, terms = 3, 448
     primes = gpu.primes[:limbs]
     order_dev = lib.Auto_order(1)
     ident = gpu.new_poly(2)
