@@ -165,14 +165,14 @@ ntt_contig_kernel(Ptr2 in, Ptr2 out, LimbBatch batch,
   // points or fewer, which the small kernel handles; so `last` is false.
   u64 x[8];
   if (!INV) {
-    // round 1: stages 0..2, elements e*32 + g straight from global memory
+    // first register pass: stages 0..2, elements e*32 + g straight from global memory
 #pragma unroll
     for (int e = 0; e < 8; e++) x[e] = src[e * 32 + g];
     fwd_round<3>(x, g, 5, kContigLog, 0, s0, blk, tw, q);
 #pragma unroll
     for (int e = 0; e < 8; e++) s[swz((e << 5) | g)] = x[e];
     __syncwarp();
-    // round 2: stages 3..5, elements (g>>2)<<5 | e<<2 | (g&3)
+    // second register pass: stages 3..5, elements (g>>2)<<5 | e<<2 | (g&3)
     int base = ((g >> 2) << 5) | (g & 3);
 #pragma unroll
     for (int e = 0; e < 8; e++) x[e] = s[swz(base | (e << 2))];
@@ -180,7 +180,7 @@ ntt_contig_kernel(Ptr2 in, Ptr2 out, LimbBatch batch,
 #pragma unroll
     for (int e = 0; e < 8; e++) s[swz(base | (e << 2))] = x[e];
     __syncwarp();
-    // round 3: stages 6..7, elements g*8 + e
+    // third register pass: stages 6..7, elements g*8 + e
     base = g << 3;
 #pragma unroll
     for (int e = 0; e < 8; e++) x[e] = s[swz(base | e)];
