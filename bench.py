@@ -83,7 +83,8 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while running."""
+    """Samples SM clocks and throttle reasons while running: one NVML session (the
+    library nvidia-smi reads from), nvidia-smi itself as the fallback."""
 
     def __init__(self, index):
         self.index = index
@@ -92,6 +93,41 @@ class ClockSampler:
         self._thread = threading.Thread(target=self._run, daemon=True)
 
     def _run(self):
+        try:
+            self._run_nvml()
+        except Exception:
+            self._run_smi()
+
+    def _run_nvml(self):
+        # one NVML session for the whole run: starting nvidia-smi again and again
+        # attaches to the driver every time and disturbs the launching thread
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            try:
+                import torch
+                prop = torch.cuda.get_device_properties(self.index)
+                bus = "%08x:%02x:%02x.0" % (prop.pci_domain_id, prop.pci_bus_id, prop.pci_device_id)
+                h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            except Exception:
+                h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            bits = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+                    0x4: "sw_power_cap"}
+            while not self._stop.is_set():
+                self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                try:
+                    mask = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    mask = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for bit, name in bits.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+                self._stop.wait(0.2)
+        finally:
+            pynvml.nvmlShutdown()
+
+    def _run_smi(self):
         q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
@@ -109,7 +145,7 @@ class ClockSampler:
                         self.reasons.add(n)
             except Exception:
                 pass
-            self._stop.wait(0.2)
+            self._stop.wait(1.0)
 
     def __enter__(self):
         self._thread.start()
