@@ -4,7 +4,10 @@
 // depend on the primes, on the 2N-th roots and on the (approximate) base
 // conversion constants; the citations name the function being matched inside
 // fhe-cmplr/rtlib/ant/.
+#include <sched.h>
+
 #include <cmath>
+#include <cstdio>
 #include <cstring>
 
 #include "runtime.h"
@@ -12,6 +15,54 @@
 namespace fhert {
 
 static Context* g_ctx = nullptr;
+
+// The thread that drives the library issues tens of thousands of launches per
+// second; it should run on the CPU cores next to its GPU.  Restricts the
+// calling thread (and what it starts later) to the cores of the GPU's NUMA
+// node that it is already allowed to use.  FHERT_NUMA_BIND=0 leaves the
+// affinity alone; so does anything unexpected in sysfs.
+static void bind_to_gpu_numa_node(int dev) {
+  const char* env = std::getenv("FHERT_NUMA_BIND");
+  if (env != nullptr && env[0] == '0') return;
+  char bus[32] = {0};
+  if (cudaDeviceGetPCIBusId(bus, sizeof(bus), dev) != cudaSuccess) return;
+  for (char* p = bus; *p; p++)
+    if (*p >= 'A' && *p <= 'F') *p = (char)(*p - 'A' + 'a');
+  char path[160];
+  std::snprintf(path, sizeof(path), "/sys/bus/pci/devices/%s/numa_node", bus);
+  FILE* f = std::fopen(path, "r");
+  if (f == nullptr) return;
+  int node = -1;
+  if (std::fscanf(f, "%d", &node) != 1) node = -1;
+  std::fclose(f);
+  if (node < 0) return;
+  std::snprintf(path, sizeof(path), "/sys/devices/system/node/node%d/cpulist", node);
+  f = std::fopen(path, "r");
+  if (f == nullptr) return;
+  cpu_set_t allowed, wanted;
+  CPU_ZERO(&wanted);
+  if (sched_getaffinity(0, sizeof(allowed), &allowed) != 0) {
+    std::fclose(f);
+    return;
+  }
+  int lo = 0, hi = 0, picked = 0;
+  while (std::fscanf(f, "%d", &lo) == 1) {  // "0-31,64-95"
+    hi = lo;
+    int ch = std::fgetc(f);
+    if (ch == '-') {
+      if (std::fscanf(f, "%d", &hi) != 1) break;
+      ch = std::fgetc(f);
+    }
+    for (int cpu = lo; cpu <= hi && cpu < CPU_SETSIZE; cpu++)
+      if (CPU_ISSET(cpu, &allowed)) {
+        CPU_SET(cpu, &wanted);
+        picked++;
+      }
+    if (ch != ',') break;
+  }
+  std::fclose(f);
+  if (picked > 0) sched_setaffinity(0, sizeof(wanted), &wanted);
+}
 
 Context* ctx() {
   FHERT_ASSERT(g_ctx != nullptr, "no context: call Prepare_context first");
@@ -431,6 +482,7 @@ Context* create_context(const CKKS_PARAMS* p) {
   {
     int dev = 0;
     CUDA_CHECK(cudaGetDevice(&dev));
+    bind_to_gpu_numa_node(dev);
     cudaMemPool_t pool;
     CUDA_CHECK(cudaDeviceGetDefaultMemPool(&pool, dev));
     uint64_t thresh = ~0ull;
