@@ -77,7 +77,16 @@ void ensure_poly(POLY res, uint32_t degree, size_t num_q, size_t num_p) {
   if (res->_data == nullptr || (num_p ? res->_num_alloc_primes != num_q + num_p
                                       : res->_num_alloc_primes < num_q)) {
     Free_poly_data(res);
-    Alloc_poly_data(res, degree, num_q, num_p);
+    // the callers write every limb they ask for, so the fresh storage is not
+    // cleared (a program's own allocations are: Alloc_poly_data)
+    Context* c              = ctx();
+    res->_ring_degree       = degree;
+    res->_num_primes        = num_q;
+    res->_num_primes_p      = num_p;
+    res->_num_alloc_primes  = num_q + num_p;
+    res->_is_ntt            = false;
+    CUDA_CHECK(cudaMallocAsync(&res->_data, (num_q + num_p) * (size_t)degree * sizeof(int64_t),
+                               c->stream));
   } else {
     res->_ring_degree  = degree;
     res->_num_primes   = num_q;
@@ -407,6 +416,8 @@ POLY Modswitch(POLY res, POLY poly) {
   FHERT_ASSERT(level >= 2, "polynomial level is too small to support modswitch");
   if (res != poly) {
     ensure_poly(res, poly->_ring_degree, level - 1, poly->_num_primes_p);
+    if (poly->_num_primes_p)  // only the Q limbs are copied: the special limbs read as zero
+      CUDA_CHECK(cudaMemsetAsync(res->_data, 0, alloc_words(res) * sizeof(int64_t), ctx()->stream));
     CUDA_CHECK(counted_copy(res->_data, poly->_data,
                                (level - 1) * poly->_ring_degree * sizeof(int64_t),
                                cudaMemcpyDeviceToDevice, ctx()->stream));
