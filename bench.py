@@ -89,6 +89,7 @@ class ClockSampler:
     def __init__(self, index):
         self.index = index
         self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.period = float(os.environ.get("BENCH_CLOCK_PERIOD_S", "0.2"))
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
 
@@ -123,7 +124,7 @@ class ClockSampler:
                 for bit, name in bits.items():
                     if mask & bit:
                         self.reasons.add(name)
-                self._stop.wait(0.2)
+                self._stop.wait(self.period)
         finally:
             pynvml.nvmlShutdown()
 
