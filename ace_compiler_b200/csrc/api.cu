@@ -85,7 +85,7 @@ void ensure_poly(POLY res, uint32_t degree, size_t num_q, size_t num_p) {
     res->_num_primes_p      = num_p;
     res->_num_alloc_primes  = num_q + num_p;
     res->_is_ntt            = false;
-    CUDA_CHECK(cudaMallocAsync(&res->_data, (num_q + num_p) * (size_t)degree * sizeof(int64_t),
+    CUDA_CHECK(dev_alloc(&res->_data, (num_q + num_p) * (size_t)degree * sizeof(int64_t),
                                c->stream));
   } else {
     res->_ring_degree  = degree;
@@ -210,7 +210,7 @@ void Alloc_poly_data(POLY poly, uint32_t degree, size_t num_q, size_t num_p) {
   poly->_num_alloc_primes = num_q + num_p;
   poly->_is_ntt           = false;
   size_t bytes            = alloc_words(poly) * sizeof(int64_t);
-  CUDA_CHECK(cudaMallocAsync(&poly->_data, bytes, c->stream));
+  CUDA_CHECK(dev_alloc(&poly->_data, bytes, c->stream));
   CUDA_CHECK(cudaMemsetAsync(poly->_data, 0, bytes, c->stream));
 }
 
@@ -218,7 +218,7 @@ void Free_poly_data(POLY poly) {
   // rns_poly.c:1319-1325
   if (poly->_data) {
     Context* c = ctx();
-    if (!pt_cache_owns(poly->_data)) CUDA_CHECK(cudaFreeAsync(poly->_data, c->stream));
+    if (!pt_cache_owns(poly->_data)) CUDA_CHECK(dev_free(poly->_data, c->stream));
     poly->_data = nullptr;
   }
   poly->_num_alloc_primes = 0;
@@ -649,7 +649,7 @@ POLY Decomp_modup(POLY res, POLY poly, uint32_t part) {
   if (part == 0 && parts > 1 && !c->draining && hw_recording(c)) {
     const size_t n = c->N, ext_limbs = level + c->K;
     int64_t*     digits = nullptr;
-    CUDA_CHECK(cudaMallocAsync(&digits, (size_t)parts * ext_limbs * n * sizeof(int64_t), c->stream));
+    CUDA_CHECK(dev_alloc(&digits, (size_t)parts * ext_limbs * n * sizeof(int64_t), c->stream));
     fhert_raise_parts(c, poly->_data, poly->_is_ntt, level, 0, parts, digits, ext_limbs, (int)level);
     for (int p = 0; p < parts; p++) {  // each digit's own limbs are the polynomial's
       size_t first = (size_t)c->alpha * p, cnt = std::min((size_t)c->alpha, level - first);
@@ -951,7 +951,7 @@ void fhert_switch_key_raised(Context* c, int64_t* out0, int64_t* out1, const int
   const uint32_t n         = c->N;
   const size_t   ext_limbs = level + c->K;
   int64_t*       acc0      = nullptr;
-  CUDA_CHECK(cudaMallocAsync(&acc0, 2 * ext_limbs * n * sizeof(int64_t), c->stream));
+  CUDA_CHECK(dev_alloc(&acc0, 2 * ext_limbs * n * sizeof(int64_t), c->stream));
   int64_t* acc1 = acc0 + ext_limbs * n;
   InnerArgs args;
   std::memset(&args, 0, sizeof(args));
@@ -974,7 +974,7 @@ void fhert_switch_key_raised(Context* c, int64_t* out0, int64_t* out1, const int
   const int64_t* x[2] = {acc0, acc1};
   const int64_t* a[2] = {add0, add1};
   fhert_mod_down_polys(c, 2, r, x, (int)level, a, level, true);
-  CUDA_CHECK(cudaFreeAsync(acc0, c->stream));
+  CUDA_CHECK(dev_free(acc0, c->stream));
 }
 
 void fhert_switch_key(Context* c, int64_t* out0, int64_t* out1, const int64_t* in, size_t level,
@@ -983,10 +983,10 @@ void fhert_switch_key(Context* c, int64_t* out0, int64_t* out1, const int64_t* i
   FHERT_ASSERT(parts <= kMaxParts, "too many digits");
   const size_t ext_limbs = level + c->K;
   int64_t*     digits    = nullptr;
-  CUDA_CHECK(cudaMallocAsync(&digits, (size_t)parts * ext_limbs * c->N * sizeof(int64_t), c->stream));
+  CUDA_CHECK(dev_alloc(&digits, (size_t)parts * ext_limbs * c->N * sizeof(int64_t), c->stream));
   fhert_raise_parts(c, in, true, level, 0, parts, digits, ext_limbs, (int)level);
   fhert_switch_key_raised(c, out0, out1, in, digits, parts, level, swk, add0, add1);
-  CUDA_CHECK(cudaFreeAsync(digits, c->stream));
+  CUDA_CHECK(dev_free(digits, c->stream));
 }
 
 CIPHER Relin(CIPHER res, CIPHER3 ciph) {
@@ -1031,7 +1031,7 @@ static CIPHER rotate_with_key(CIPHER res, CIPHER ciph, int32_t rot_idx, uint32_t
   size_t   level = Level(ciph);
   size_t   words = level * c->N;
   int64_t* t     = nullptr;
-  CUDA_CHECK(cudaMallocAsync(&t, 2 * words * sizeof(int64_t), c->stream));
+  CUDA_CHECK(dev_alloc(&t, 2 * words * sizeof(int64_t), c->stream));
   fhert_switch_key(c, t, t + words, ciph->_c1_poly._data, level, Swk(true, rot_idx),
              ciph->_c0_poly._data, nullptr);
   if (res != ciph)
@@ -1039,7 +1039,7 @@ static CIPHER rotate_with_key(CIPHER res, CIPHER ciph, int32_t rot_idx, uint32_t
   LimbBatch one = poly_batch(c, &res->_c0_poly, &res->_c0_poly, nullptr, level, 0);
   launch_automorphism(ptr2(res->_c0_poly._data, res->_c1_poly._data), ptr2(t, t + words),
                       auto_table(c, k), both_polys(one));
-  CUDA_CHECK(cudaFreeAsync(t, c->stream));
+  CUDA_CHECK(dev_free(t, c->stream));
   return res;
 }
 
@@ -1051,8 +1051,8 @@ void Rotate_batch_ciph(CIPHER res_arr, CIPHER ciph, const int32_t* rot_idx, uint
   size_t   level = Level(ciph), words = level * c->N, ext_limbs = level + c->K;
   const int parts = (int)std::min<size_t>((level + c->alpha - 1) / c->alpha, c->dnum);
   int64_t *digits = nullptr, *t = nullptr;
-  CUDA_CHECK(cudaMallocAsync(&digits, (size_t)parts * ext_limbs * c->N * sizeof(int64_t), c->stream));
-  CUDA_CHECK(cudaMallocAsync(&t, 2 * words * sizeof(int64_t), c->stream));
+  CUDA_CHECK(dev_alloc(&digits, (size_t)parts * ext_limbs * c->N * sizeof(int64_t), c->stream));
+  CUDA_CHECK(dev_alloc(&t, 2 * words * sizeof(int64_t), c->stream));
   fhert_raise_parts(c, ciph->_c1_poly._data, true, level, 0, parts, digits, ext_limbs, (int)level);
   for (uint32_t i = 0; i < count; i++) {
     CIPHER out = &res_arr[i];
@@ -1068,8 +1068,8 @@ void Rotate_batch_ciph(CIPHER res_arr, CIPHER ciph, const int32_t* rot_idx, uint
     launch_automorphism(ptr2(out->_c0_poly._data, out->_c1_poly._data), ptr2(t, t + words),
                         auto_table(c, auto_index_for(c, rot_idx[i])), both_polys(one));
   }
-  CUDA_CHECK(cudaFreeAsync(t, c->stream));
-  CUDA_CHECK(cudaFreeAsync(digits, c->stream));
+  CUDA_CHECK(dev_free(t, c->stream));
+  CUDA_CHECK(dev_free(digits, c->stream));
 }
 
 CIPHER Rotate_ciph(CIPHER res, CIPHER ciph, int32_t rot_idx) {

@@ -446,9 +446,9 @@ struct DevBuf {  // stream-ordered scratch
   int64_t* p = nullptr;
   Context* c;
   DevBuf(Context* ctx_, size_t words) : c(ctx_) {
-    CUDA_CHECK(cudaMallocAsync(&p, words * sizeof(int64_t), c->stream));
+    CUDA_CHECK(dev_alloc(&p, words * sizeof(int64_t), c->stream));
   }
-  ~DevBuf() { cudaFreeAsync(p, c->stream); }
+  ~DevBuf() { dev_free(p, c->stream); }
   DevBuf(const DevBuf&)            = delete;
   DevBuf& operator=(const DevBuf&) = delete;
 };

@@ -21,7 +21,7 @@ POLY_ARR Alloc_polys(uint32_t cnt, uint32_t degree, size_t num_q, size_t num_p) 
   POLY_ARR res   = (POLY_ARR)std::calloc(cnt, sizeof(POLYNOMIAL));
   size_t   words = (num_q + num_p) * (size_t)degree;
   int64_t* data  = nullptr;
-  CUDA_CHECK(cudaMallocAsync(&data, words * cnt * sizeof(int64_t), c->stream));
+  CUDA_CHECK(dev_alloc(&data, words * cnt * sizeof(int64_t), c->stream));
   CUDA_CHECK(cudaMemsetAsync(data, 0, words * cnt * sizeof(int64_t), c->stream));
   for (uint32_t i = 0; i < cnt; i++) {
     res[i]._ring_degree      = degree;
@@ -37,7 +37,7 @@ POLY_ARR Alloc_polys(uint32_t cnt, uint32_t degree, size_t num_q, size_t num_p) 
 void Free_polys(POLY_ARR polys) {  // include/poly/rns_poly.h:182-188
   FHERT_ASSERT(polys != nullptr, "null polynomial array");
   Context* c = ctx();
-  if (polys[0]._data) CUDA_CHECK(cudaFreeAsync(polys[0]._data, c->stream));
+  if (polys[0]._data) CUDA_CHECK(dev_free(polys[0]._data, c->stream));
   std::free(polys);
 }
 

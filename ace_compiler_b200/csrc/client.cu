@@ -122,7 +122,7 @@ LimbBatch dense_batch(Context* c, size_t level, size_t num_p) {
 // device copy of a host sample vector, freed in stream order by the caller
 int64_t* upload_samples(Context* c, const std::vector<int64_t>& v) {
   int64_t* d = nullptr;
-  CUDA_CHECK(cudaMallocAsync(&d, v.size() * sizeof(int64_t), c->stream));
+  CUDA_CHECK(dev_alloc(&d, v.size() * sizeof(int64_t), c->stream));
   CUDA_CHECK(counted_copy(d, v.data(), v.size() * sizeof(int64_t), cudaMemcpyHostToDevice,
                              c->stream));
   // the host vector may go out of scope before the copy is consumed
@@ -137,7 +137,7 @@ void sample_error_poly(Context* c, POLY e) {
   sample_triangle(tri.data(), c->N);
   int64_t* d = upload_samples(c, tri);
   launch_small_to_rns(e->_data, d, dense_batch(c, e->_num_primes, e->_num_primes_p));
-  CUDA_CHECK(cudaFreeAsync(d, c->stream));
+  CUDA_CHECK(dev_free(d, c->stream));
   e->_is_ntt = false;
 }
 

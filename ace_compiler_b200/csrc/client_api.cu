@@ -183,7 +183,7 @@ void encode_vector(Context* c, PLAIN plain, std::vector<cplx>& values, uint32_t 
   init_plain(c, plain, level, std::pow(delta, (double)sf_degree), sf_degree, slots, num_p);
   int64_t* d_msg = nullptr;
   u64*     d_pow = nullptr;
-  CUDA_CHECK(cudaMallocAsync(&d_msg, n * sizeof(int64_t), c->stream));
+  CUDA_CHECK(dev_alloc(&d_msg, n * sizeof(int64_t), c->stream));
   // inverse embedding, scaling and rounding run on the device with the host
   // routine's arithmetic (encode_gpu.cu)
   encode_message_on_device(c, values.data(), values.size(), slots, d_msg);
@@ -196,14 +196,14 @@ void encode_vector(Context* c, PLAIN plain, std::vector<cplx>& values, uint32_t 
       for (uint32_t d = 2; d < sf_degree; d++) p = mulmod(p, (u64)(int64_t)delta % q, q);
       powp[i] = p;
     }
-    CUDA_CHECK(cudaMallocAsync(&d_pow, powp.size() * sizeof(u64), c->stream));
+    CUDA_CHECK(dev_alloc(&d_pow, powp.size() * sizeof(u64), c->stream));
     CUDA_CHECK(counted_copy(d_pow, powp.data(), powp.size() * sizeof(u64),
                                cudaMemcpyHostToDevice, c->stream));
   }
   launch_encode_split(plain->_poly._data, d_msg, d_pow, q_batch(level, num_p, c->L));
   if (d_pow) CUDA_CHECK(cudaStreamSynchronize(c->stream));  // powp lives on the host stack
-  CUDA_CHECK(cudaFreeAsync(d_msg, c->stream));
-  if (d_pow) CUDA_CHECK(cudaFreeAsync(d_pow, c->stream));
+  CUDA_CHECK(dev_free(d_msg, c->stream));
+  if (d_pow) CUDA_CHECK(dev_free(d_pow, c->stream));
   plain->_poly._is_ntt = false;
   Conv_poly2ntt_inplace(&plain->_poly);
 }
@@ -307,13 +307,13 @@ void error_poly(Context* c, POLY e, size_t level) {
   std::vector<int64_t> tri(c->N);
   sample_triangle(tri.data(), c->N);
   int64_t* d = nullptr;
-  CUDA_CHECK(cudaMallocAsync(&d, c->N * sizeof(int64_t), c->stream));
+  CUDA_CHECK(dev_alloc(&d, c->N * sizeof(int64_t), c->stream));
   CUDA_CHECK(counted_copy(d, tri.data(), c->N * sizeof(int64_t), cudaMemcpyHostToDevice,
                              c->stream));
   Alloc_poly_data(e, c->N, level, 0);
   launch_small_to_rns(e->_data, d, q_batch(level));
   CUDA_CHECK(cudaStreamSynchronize(c->stream));
-  CUDA_CHECK(cudaFreeAsync(d, c->stream));
+  CUDA_CHECK(dev_free(d, c->stream));
   e->_is_ntt = false;
 }
 

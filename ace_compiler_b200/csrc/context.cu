@@ -8,6 +8,8 @@
 
 #include <cmath>
 #include <cstdio>
+#include <unordered_map>
+#include <vector>
 #include <cstring>
 
 #include "runtime.h"
@@ -477,6 +479,10 @@ Context* create_context(const CKKS_PARAMS* p) {
     init_modulus(&c->moduli[i], c->primes[i]);
   }
 
+  // FHERT_SPIN=1: the driver's waits of this process busy-wait instead of sleeping
+  if (const char* spin = std::getenv("FHERT_SPIN")) {
+    if (spin[0] == '1' && cudaSetDeviceFlags(cudaDeviceScheduleSpin) != cudaSuccess) cudaGetLastError();
+  }
   CUDA_CHECK(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
   // keep freed blocks cached in the stream-ordered pool
   {
@@ -579,6 +585,9 @@ void destroy_context() {
   free_bootstrap(c);
   free_keys(c);
   release_prng();
+  if (c->scratch) dev_free(c->scratch, c->stream);
+  c->scratch = nullptr;
+  dev_release_all(c->stream);
   cudaStreamSynchronize(c->stream);
   cudaFree(c->d_mod);
   cudaFree(c->d_fwd);
@@ -678,12 +687,75 @@ size_t prof_end(char* buf, size_t cap) {
   return off;
 }
 
+// ---- device memory kept in per-size lists -----------------------------------
+namespace {
+struct DevPool {
+  std::unordered_map<size_t, std::vector<void*>> free_by_size;
+  std::unordered_map<void*, size_t>              size_of;
+  int                                            enabled = -1;
+  size_t                                         held = 0;  // bytes waiting in the lists
+  size_t                                         cap  = (size_t)32 << 30;
+};
+DevPool g_pool;
+bool pool_enabled() {
+  if (g_pool.enabled < 0) {
+    const char* e  = std::getenv("FHERT_POOL");
+    g_pool.enabled = !(e != nullptr && e[0] == '0');
+    if (const char* mb = std::getenv("FHERT_POOL_MB"))
+      g_pool.cap = (size_t)std::strtoull(mb, nullptr, 10) << 20;
+  }
+  return g_pool.enabled != 0;
+}
+}  // namespace
+
+cudaError_t dev_alloc(void** ptr, size_t bytes, cudaStream_t stream) {
+  if (!pool_enabled()) return cudaMallocAsync(ptr, bytes, stream);
+  if (bytes == 0) bytes = 256;
+  bytes = (bytes + 255) & ~(size_t)255;
+  auto it = g_pool.free_by_size.find(bytes);
+  if (it != g_pool.free_by_size.end() && !it->second.empty()) {
+    *ptr = it->second.back();
+    it->second.pop_back();
+    g_pool.held -= bytes;
+    return cudaSuccess;
+  }
+  cudaError_t err = cudaMallocAsync(ptr, bytes, stream);
+  if (err == cudaErrorMemoryAllocation) {  // make room with what the lists hold
+    cudaGetLastError();
+    dev_release_all(stream);
+    cudaStreamSynchronize(stream);
+    err = cudaMallocAsync(ptr, bytes, stream);
+  }
+  if (err == cudaSuccess) g_pool.size_of[*ptr] = bytes;
+  return err;
+}
+
+cudaError_t dev_free(void* ptr, cudaStream_t stream) {
+  if (ptr == nullptr) return cudaSuccess;
+  auto it = g_pool.size_of.find(ptr);
+  if (it == g_pool.size_of.end()) return cudaFreeAsync(ptr, stream);  // not from the lists
+  g_pool.free_by_size[it->second].push_back(ptr);
+  g_pool.held += it->second;
+  if (g_pool.held > g_pool.cap) dev_release_all(stream);  // sizes no longer in use pile up
+  return cudaSuccess;
+}
+
+void dev_release_all(cudaStream_t stream) {
+  for (auto& kv : g_pool.free_by_size)
+    for (void* p : kv.second) {
+      g_pool.size_of.erase(p);
+      cudaFreeAsync(p, stream);
+    }
+  g_pool.free_by_size.clear();
+  g_pool.held = 0;
+}
+
 int64_t* scratch(size_t words) {
   Context* c = ctx();
   if (c->scratch_words < words) {
     // the old block may still be in use by queued kernels: free it in stream order
-    if (c->scratch) CUDA_CHECK(cudaFreeAsync(c->scratch, c->stream));
-    CUDA_CHECK(cudaMallocAsync(&c->scratch, words * sizeof(int64_t), c->stream));
+    if (c->scratch) CUDA_CHECK(dev_free(c->scratch, c->stream));
+    CUDA_CHECK(dev_alloc(&c->scratch, words * sizeof(int64_t), c->stream));
     c->scratch_words = words;
   }
   return c->scratch;

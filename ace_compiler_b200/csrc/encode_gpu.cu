@@ -105,7 +105,7 @@ void encode_message_on_device(Context* c, const std::complex<double>* values, si
   int            lg = 0;
   while ((1u << lg) < slots) lg++;
   double2* v = nullptr;
-  CUDA_CHECK(cudaMallocAsync(&v, (size_t)slots * sizeof(double2), c->stream));
+  CUDA_CHECK(dev_alloc(&v, (size_t)slots * sizeof(double2), c->stream));
   CUDA_CHECK(cudaMemsetAsync(v, 0, (size_t)slots * sizeof(double2), c->stream));
   // std::complex<double> is two doubles, real part first
   CUDA_CHECK(counted_copy(v, values, count * sizeof(double2), cudaMemcpyHostToDevice, c->stream));
@@ -120,7 +120,7 @@ void encode_message_on_device(Context* c, const std::complex<double>* values, si
   prof_after(KID_ENCODE, 1);
   c->launches += lg + 1;
   CUDA_CHECK(cudaGetLastError());
-  CUDA_CHECK(cudaFreeAsync(v, c->stream));
+  CUDA_CHECK(dev_free(v, c->stream));
 }
 
 }  // namespace fhert

@@ -188,7 +188,7 @@ HwQueue* queue_of(Context* c) {
 u64* scratch_limb(Context* c, HwQueue* q) {
   if (q->arena_used == kArena) {
     u64* p = nullptr;
-    CUDA_CHECK(cudaMallocAsync(&p, (size_t)kArena * c->N * sizeof(u64), c->stream));
+    CUDA_CHECK(dev_alloc(&p, (size_t)kArena * c->N * sizeof(u64), c->stream));
     q->arenas.push_back(p);
     q->arena_used = 0;
   }
@@ -348,9 +348,9 @@ void hw_replay(Context* c) {
     pack.add_chain(home.data(), &self, 1);
   }
   pack.flush();
-  for (u64* p : q->arenas) CUDA_CHECK(cudaFreeAsync(p, c->stream));
+  for (u64* p : q->arenas) CUDA_CHECK(dev_free(p, c->stream));
   q->arenas.clear();
-  for (void* p : q->borrowed) CUDA_CHECK(cudaFreeAsync(p, c->stream));
+  for (void* p : q->borrowed) CUDA_CHECK(dev_free(p, c->stream));
   q->borrowed.clear();
   c->raised.valid = false;  // its digits were among the borrowed memory
   q->arena_used = kArena;

@@ -231,6 +231,21 @@ LimbBatch poly_batch(Context* c, POLY res, POLY a, POLY b, size_t level, size_t 
 LimbBatch both_polys(const LimbBatch& one);
 void      ensure_poly(POLY res, uint32_t degree, size_t num_q, size_t num_p);
 
+// ---- context.cu: device memory of the library stream ----
+// All device work of the library runs on one stream, so a block handed back is
+// safe to hand out again at once (whatever uses it next is queued behind
+// whatever used it last).  Blocks are kept in per-size lists and only a size
+// never seen before reaches the driver: the tens of thousands of polynomial
+// allocations of a program cost no driver call and no pool bookkeeping.
+// FHERT_POOL=0 sends every request to cudaMallocAsync / cudaFreeAsync instead.
+cudaError_t dev_alloc(void** ptr, size_t bytes, cudaStream_t stream);
+cudaError_t dev_free(void* ptr, cudaStream_t stream);
+template <typename T>
+inline cudaError_t dev_alloc(T** ptr, size_t bytes, cudaStream_t stream) {
+  return dev_alloc(reinterpret_cast<void**>(ptr), bytes, stream);
+}
+void dev_release_all(cudaStream_t stream);  // gives every kept block back to the driver
+
 // ---- encode_gpu.cu ----
 // inverse embedding, scaling and rounding of `count` complex slot values (host)
 // into the message polynomial d_msg (N int64 on the device)

@@ -84,9 +84,9 @@ void* Fhert_shard_begin(const int64_t* c1, size_t level, int rank, int world, in
   s->qb    = (int)((level + world - 1) / world);
   s->pb    = (c->K + world - 1) / world;
   const size_t n = c->N, ext = level + c->K;
-  CUDA_CHECK(cudaMallocAsync(&s->ext, (size_t)s->parts * ext * n * sizeof(int64_t), c->stream));
-  CUDA_CHECK(cudaMallocAsync(&s->acc, 2 * ext * n * sizeof(int64_t), c->stream));
-  CUDA_CHECK(cudaMallocAsync(&s->conv, 2 * level * n * sizeof(int64_t), c->stream));
+  CUDA_CHECK(dev_alloc(&s->ext, (size_t)s->parts * ext * n * sizeof(int64_t), c->stream));
+  CUDA_CHECK(dev_alloc(&s->acc, 2 * ext * n * sizeof(int64_t), c->stream));
+  CUDA_CHECK(dev_alloc(&s->conv, 2 * level * n * sizeof(int64_t), c->stream));
   // own Q limbs of c1 to coefficient form, straight into this rank's block of
   // the exchange buffer (limb i sits at index i of the gathered array)
   std::vector<LimbRef> own;
@@ -237,9 +237,9 @@ void Fhert_shard_end(void* state, const int64_t* c0, const int64_t* gather_p0,
                                     (uint8_t)(g ? 4 : 0)};
   launch_automorphism(ptr2(out0, out1), ptr2(s->conv), auto_table(c, k), ab);
 
-  CUDA_CHECK(cudaFreeAsync(s->ext, c->stream));
-  CUDA_CHECK(cudaFreeAsync(s->acc, c->stream));
-  CUDA_CHECK(cudaFreeAsync(s->conv, c->stream));
+  CUDA_CHECK(dev_free(s->ext, c->stream));
+  CUDA_CHECK(dev_free(s->acc, c->stream));
+  CUDA_CHECK(dev_free(s->conv, c->stream));
   delete s;
 }
 
