@@ -432,6 +432,7 @@ def run_resnet20(args):
         barrier()
     host_cpu_s = (time.process_time() - cpu0) / args.steps
     ms_total = E0.elapsed_time(E1)
+    image_ms = [round(a.elapsed_time(b), 1) for a, b in events]
     ms_graph = sum(a.elapsed_time(b) for a, b in events)
     launches = lib.Fhert_kernel_launches() - launches0
     h2d1, d2h1 = transfer()
@@ -515,6 +516,7 @@ def run_resnet20(args):
                                                     "not this program's 51/46-bit parameters, "
                                                     "so vs_baseline stays null)",
                        "setup_s": round(setup_s, 1),
+                       "image_ms_this_rank": image_ms,
                        "s_per_image_weights_encoded_every_image": round(ms_uncached / 1e3, 3),
                        "host_cpu_s_per_image": round(host_cpu_s, 3),
                        "weight_plaintexts_resident": {"entries": stats[0].value,
