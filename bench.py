@@ -461,6 +461,17 @@ def run_resnet20(args):
     for ln in buf.raw[:used].decode().splitlines():
         name, cnt, limbs, ms = ln.split()
         rows[name] = {"launches": int(cnt), "limbs": int(limbs), "ms": float(ms)}
+    # BENCH_PROFILE_IMAGES=k: k more profiled images, kernel-time sum against the
+    # image's own device time, to tell a slow GPU from a starved one (stderr)
+    for k in range(int(os.environ.get("BENCH_PROFILE_IMAGES", "0"))):
+        ev = []
+        lib.Fhert_profile_begin()
+        one_image(ev)
+        n_used = lib.Fhert_profile_end(buf, len(buf))
+        barrier()
+        ksum = sum(float(ln.split()[3]) for ln in buf.raw[:n_used].decode().splitlines())
+        print(f"profiled image {k}: kernels {ksum:.1f} ms, image {ev[0][0].elapsed_time(ev[0][1]):.1f} ms",
+              file=sys.stderr)
     stats = [C.c_size_t() for _ in range(4)]
     lib.Fhert_pt_cache_stats(*[C.byref(x) for x in stats])
 
