@@ -3,12 +3,21 @@
 // Rescale (api.cu) borrows its working storage -- the coefficient form of the
 // limb being dropped plus one lifted copy per remaining limb -- from a
 // stream-ordered allocation that grows on demand.  Some hosts cannot tolerate
-// that: code running while a CUDA graph is being captured, real-time loops
-// that have pinned down their memory budget, or embedders whose policy forbids
-// the driver allocator after start-up.  Fhert_rescale_static does the same
-// arithmetic with working storage that is part of the library image: a
-// file-scope device array of fixed size that every GPU loading the library
-// carries until the process exits.
+// that: serving loops that have pinned down their device-memory budget at
+// start-up and must not see it move, embedders whose policy forbids the driver
+// allocator once the process is running, and callers sharing the GPU with
+// another tenant whose allocations they must not disturb.
+// Fhert_rescale_static does the same arithmetic with working storage that is
+// part of the library image: a file-scope device array of fixed size that
+// every GPU loading the library carries until the process exits.
+//
+// The guarantee "no allocator is called" holds for the call itself.  Work that
+// earlier entry points deferred (a Rescale / Mod_down waiting for its sibling,
+// recorded Hw_* calls) would run first and does allocate, so the call refuses
+// with FHERT_STATIC_PENDING_WORK while such work is waiting: finish it with
+// Fhert_sync (or any other entry point) before the phase that must not
+// allocate.  With Fhert_profile_begin active every launch also records two
+// CUDA events, created on first use.  A CUDA launch error still aborts.
 #include "runtime.h"
 
 namespace fhert {
@@ -72,6 +81,12 @@ extern "C" int Fhert_rescale_static(int64_t* res, const int64_t* poly, size_t le
                  "working storage, the built-in array holds %zu; use Rescale instead\n",
                  level, n, level * n, (size_t)kStaticScratchWords);
     return FHERT_STATIC_TOO_LARGE;
+  }
+  if (c->pair_wait.kind != 0 || c->hw_pending) {
+    std::fprintf(stderr,
+                 "libFHErt_b200: Fhert_rescale_static: deferred work of earlier calls is waiting "
+                 "and would allocate; call Fhert_sync first\n");
+    return FHERT_STATIC_PENDING_WORK;
   }
   int      status = FHERT_STATIC_OK;
   int64_t* sc     = static_scratch_for_current_device(&status);

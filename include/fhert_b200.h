@@ -263,24 +263,31 @@ POLY   Dot_prod(POLY res, POLY a, POLY b, size_t parts);
 POLY   Automorphism_transform(POLY res, POLY poly, int64_t* order);
 
 /* No counterpart in the CPU runtime.  Rescale for hosts that may not allocate
- * device memory once they are running (stream capture in progress, fixed
- * memory budgets, allocator-free embedders): same result as Rescale, but the
- * working storage is a 20 MiB device array built into the library instead of
- * a stream-ordered allocation.  `poly` holds `level` limbs in NTT form, `res`
- * receives level-1 limbs (both device buffers of the caller, limb-major; res
- * may alias poly).  Returns 0, or a FHERT_STATIC_* code after printing why:
- * level * N above Fhert_rescale_static_capacity() words is refused.  The
- * first call on each device resolves the array's device address and should
- * therefore be made before any stream capture starts.  The entry point itself
- * calls no allocator.  All calls share the one array: it needs no clearing
- * between calls, but two calls that overlap on the GPU (different streams or
- * host threads) race on it. */
+ * device memory once they are running (a serving loop with a pinned-down
+ * memory budget, an embedder whose policy forbids the driver allocator after
+ * start-up, a process sharing the GPU with another tenant): same result as
+ * Rescale, but the working storage is a 20 MiB device array built into the
+ * library instead of a stream-ordered allocation.  `poly` holds `level` limbs
+ * in NTT form, `res` receives level-1 limbs (both device buffers of the
+ * caller, limb-major; res may alias poly).  Returns 0, or a FHERT_STATIC_*
+ * code after printing why: level * N above Fhert_rescale_static_capacity()
+ * words is refused, and so is a call made while earlier entry points have
+ * deferred work waiting (a Rescale / Mod_down without its sibling, recorded
+ * Hw_* calls): that work allocates when it runs, so finish it with Fhert_sync
+ * first.  The first call on each device resolves the array's device address
+ * and should therefore be made before any stream capture starts.  The entry
+ * point itself calls no allocator (with Fhert_profile_begin active each launch
+ * records two CUDA events, created on first use).  All calls share the one
+ * array: it needs no clearing between calls, but two calls that overlap on
+ * the GPU (different streams or host threads) race on it.  A failing CUDA
+ * launch aborts like everywhere else in the library. */
 enum {
   FHERT_STATIC_OK = 0,
   FHERT_STATIC_NO_CONTEXT = 1,
   FHERT_STATIC_BAD_ARGUMENT = 2,
   FHERT_STATIC_TOO_LARGE = 3,
-  FHERT_STATIC_NO_DEVICE = 4
+  FHERT_STATIC_NO_DEVICE = 4,
+  FHERT_STATIC_PENDING_WORK = 5
 };
 int    Fhert_rescale_static(int64_t* res, const int64_t* poly, size_t level);
 size_t Fhert_rescale_static_capacity(void); /* words of built-in storage */
