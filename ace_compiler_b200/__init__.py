@@ -111,6 +111,7 @@ SIGNATURES = {
     "Hw_modsub": (C.c_void_p, [I64P, I64P, I64P, MODP, C.c_uint32]),
     "Hw_modmul": (C.c_void_p, [I64P, I64P, I64P, MODP, C.c_uint32]),
     "Hw_modmuladd": (C.c_void_p, [I64P, I64P, I64P, MODP, C.c_uint32]),
+    "Hw_modmuladd_scalar": (C.c_void_p, [I64P, I64P, C.c_int64, MODP, C.c_uint32]),
     "Hw_modadd_scalar": (C.c_void_p, [I64P, I64P, C.c_int64, MODP, C.c_uint32]),
     "Hw_modmul_scalar": (C.c_void_p, [I64P, I64P, C.c_int64, MODP, C.c_uint32]),
     "Hw_rotate": (C.c_void_p, [I64P, I64P, I64P, MODP, C.c_uint32]),
@@ -130,6 +131,8 @@ SIGNATURES = {
     "Mod_down": (POLY, [POLY, POLY]),
     "Extend": (POLY, [POLY, POLY]),
     "Dot_prod": (POLY, [POLY, POLY, POLY, C.c_size_t]),
+    "Mod_down_rescale": (POLY, [POLY, POLY]),
+    "Chk_level": (None, [POLY, POLY, POLY]),
     "Automorphism_transform": (POLY, [POLY, POLY, I64P]),
     "Fhert_rescale_static": (C.c_int, [I64P, I64P, C.c_size_t]),
     "Fhert_rescale_static_capacity": (C.c_size_t, []),

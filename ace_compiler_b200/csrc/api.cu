@@ -342,6 +342,13 @@ int64_t* Hw_modadd_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint3
 int64_t* Hw_modmul_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint32_t degree) {
   return hw_binary(EW_MUL_SCALAR, res, a, a, s, m, degree);
 }
+int64_t* Hw_modmuladd_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint32_t degree) {
+  // hal.c:109-121; no compiled program emits it, so it is launched at once
+  Context* c = ctx();
+  FHERT_ASSERT(degree == c->N, "degree mismatch");
+  launch_elementwise(EW_MULADD_SCALAR, ptr2(res), ptr2(a), ptr2(a), s, single(prime_index_of(c, m)));
+  return res;
+}
 int64_t* Hw_rotate(int64_t* res, int64_t* val, int64_t* order, MODULUS* m, uint32_t degree) {
   Context* c = ctx_noflush();
   FHERT_ASSERT(degree == c->N, "degree mismatch");
@@ -445,6 +452,23 @@ void fhert_rescale_polys(Context* c, int npoly, int64_t* const res[2],
   launch_ntt(ptr2(poly[0], poly[1]), ptr2(sc), lb, true);
   LimbBatch bt;
   bt.count = npoly * l;
+  if (ntt_can_fuse()) {
+    // lift inside the first pass of the forward transform, combine inside its last
+    for (int g = 0; g < npoly; g++)
+      for (int i = 0; i < l; i++) {
+        uint8_t sel = (uint8_t)(g ? (2 | 4) : 0);  // aux (poly) and res from the second base
+        bt.limb[g * l + i] = LimbRef{(uint16_t)g, (uint16_t)i, (uint16_t)i, (uint8_t)i, sel};
+      }
+    NttFuse f;
+    f.pro_mul  = c->d_ql_neg + (size_t)l * c->L;
+    f.pro_mod  = c->d_ql_mod + (size_t)l * c->L;
+    f.q_last   = c->primes[l];
+    f.epi_kind = 1;
+    f.epi_mul  = c->d_ql_inv + (size_t)l * c->L;
+    f.aux      = ptr2(poly[0], poly[1]);
+    launch_ntt_fused(ptr2(sc), sc + (size_t)npoly * n, ptr2(res[0], res[1]), bt, f);
+    return;
+  }
   for (int g = 0; g < npoly; g++)
     for (int i = 0; i < l; i++) {
       uint16_t t = (uint16_t)(npoly + g * l + i);
@@ -732,6 +756,24 @@ void fhert_mod_down_polys(Context* c, int npoly, int64_t* const res[2],
     cg.skip_len    = 0;
   }
   launch_base_conv(args);
+  if (is_ntt && ntt_can_fuse()) {
+    // the ModDown tail runs inside the last pass of the forward transform
+    LimbBatch out;
+    out.count = npoly * (int)level;
+    for (int g = 0; g < npoly; g++)
+      for (int i = 0; i < (int)level; i++) {
+        uint8_t sel = (uint8_t)(g ? (2 | 4) : 0);  // x (and addend) and res from the second base
+        out.limb[g * level + i] =
+            LimbRef{(uint16_t)(g * level + i), (uint16_t)i, (uint16_t)i, (uint8_t)i, sel};
+      }
+    NttFuse f;
+    f.epi_kind = 2;
+    f.epi_mul  = c->d_p_inv;
+    f.aux      = ptr2(ext[0], npoly > 1 ? ext[1] : nullptr);
+    if (add) f.add = ptr2(add[0], npoly > 1 ? add[1] : nullptr);
+    launch_ntt_fused(ptr2(conv), conv, ptr2(res[0], npoly > 1 ? res[1] : nullptr), out, f);
+    return;
+  }
   if (is_ntt) {
     LimbBatch out;
     out.count = npoly * (int)level;
@@ -763,6 +805,50 @@ POLY Mod_down(POLY res, POLY poly) {
   pair_submit(1, res->_data, poly->_data, level, (int)p_offset(poly), poly->_is_ntt);
   res->_is_ntt = poly->_is_ntt;
   return res;
+}
+
+POLY Mod_down_rescale(POLY res, POLY poly) {
+  // rns_poly.c:531-603: ModDown and Rescale in one step, computed in coefficient
+  // form; like the CPU runtime it leaves `poly` in coefficient form.
+  Context*       c     = ctx();
+  const size_t   level = poly->_num_primes, n = c->N;
+  const int      K     = c->K;
+  FHERT_ASSERT(res->_data && res->_num_primes == level && level > 1 &&
+                   poly->_num_primes_p == (size_t)K && res->_num_primes_p == 0,
+               "Mod_down_rescale: size not match");
+  if (poly->_is_ntt) Conv_ntt2poly_inplace(poly);
+  int64_t* conv = scratch(level * n);
+  ConvArgs args;
+  args.groups     = 1;
+  args.level      = (int)level;
+  args.out_total  = (int)level;
+  args.p_limb     = 0;
+  args.in_stride  = 1;
+  args.out_stride = K;
+  ConvGroup& cg   = args.g[0];
+  cg.in           = reinterpret_cast<const u64*>(poly->_data + p_offset(poly) * n);
+  cg.out          = reinterpret_cast<u64*>(conv);
+  cg.inv          = c->d_phat_inv;
+  cg.mat          = c->d_phat_mod_q;
+  cg.first_limb   = 0;
+  cg.first_prime  = c->L;
+  cg.count        = K;
+  cg.skip_start   = 0;
+  cg.skip_len     = 0;
+  launch_base_conv(args);
+  launch_moddown_rescale(res->_data, poly->_data, conv, (int)level);
+  res->_num_primes = level - 1;
+  res->_is_ntt     = false;
+  Conv_poly2ntt_inplace(res);
+  return res;
+}
+
+void Chk_level(POLY res, POLY p0, POLY p1) {
+  // rns_poly.c:606-613: a diagnostic, it only prints
+  if (res->_num_primes != p0->_num_primes || res->_num_primes_p != p0->_num_primes_p)
+    std::printf("level not match\n");
+  if (p1 && (res->_num_primes != p1->_num_primes || res->_num_primes_p != p1->_num_primes_p))
+    std::printf("level not match\n");
 }
 
 POLY Extend(POLY res, POLY poly) {

@@ -40,7 +40,7 @@ ew_kernel(Ptr2 res, Ptr2 a, Ptr2 b, u64 scalar, LimbBatch batch,
   const u64*       pb = sel_b(b, lr, n);
   u64*             pr = sel_d(res, lr, n);
   u64              sc = 0;
-  if (OP == EW_ADD_SCALAR || OP == EW_MUL_SCALAR) {
+  if (OP == EW_ADD_SCALAR || OP == EW_MUL_SCALAR || OP == EW_MULADD_SCALAR) {
     // scalars arrive as signed 64-bit values; bring into [0, q)
     int64_t s = (int64_t)scalar % (int64_t)m.q;
     sc        = s < 0 ? (u64)(s + (int64_t)m.q) : (u64)s;
@@ -52,6 +52,7 @@ ew_kernel(Ptr2 res, Ptr2 a, Ptr2 b, u64 scalar, LimbBatch batch,
     else if (OP == EW_MUL) r = mul_mod(x, pb[i], m);
     else if (OP == EW_MULADD) r = add_mod(pr[i], mul_mod(x, pb[i], m), m.q);
     else if (OP == EW_ADD_SCALAR) r = add_mod(x, sc, m.q);
+    else if (OP == EW_MULADD_SCALAR) r = add_mod(pr[i], mul_mod(x, sc, m), m.q);
     else r = mul_mod(x, sc, m);
     pr[i] = r;
   }
@@ -270,6 +271,41 @@ moddown_combine_kernel(ModDownTail a, const Twiddle* __restrict__ p_inv,
   }
 }
 
+// ---- fused ModDown + Rescale tail, coefficient form (rns_poly.c:556-596) -----
+
+// Sub_mul_const_mod of the CPU runtime (modular.h:266-276) on operands where
+// val2 may exceed the modulus: the signed difference gets the modulus added
+// once when negative and may stay negative; the Shoup product then runs on its
+// two's-complement image exactly as the 128-bit host arithmetic does.
+__device__ __forceinline__ u64 sub_mul_const_exact(u64 v1, u64 v2, u64 w, u64 wp, u64 q) {
+  long long s = (long long)v1 - (long long)v2;
+  if (s < 0) s += (long long)q;
+  u64 lo = (u64)s;
+  u64 qt = __umul64hi(lo, wp) - (s < 0 ? wp : 0);  // ((2^128 + s) * wp >> 64) mod 2^64
+  u64 y  = lo * w - qt * q;
+  return y >= q ? y - q : y;
+}
+
+__global__ void __launch_bounds__(kThreads)
+moddown_rescale_kernel(u64* __restrict__ res, const u64* __restrict__ x,
+                       const u64* __restrict__ t, int last, const Twiddle* __restrict__ p_inv,
+                       const Twiddle* __restrict__ ql_inv_row,
+                       const DevModulus* __restrict__ mods, uint32_t n) {
+  const int     i    = blockIdx.y;  // output limb, i < last
+  const u64     q    = mods[i].q, ql = mods[last].q;
+  const Twiddle pi   = p_inv[i], pl = p_inv[last], wi = ql_inv_row[i];
+  const u64*    xi   = x + (size_t)i * n;
+  const u64*    ti   = t + (size_t)i * n;
+  const u64*    xl   = x + (size_t)last * n;
+  const u64*    tl   = t + (size_t)last * n;
+  u64*          ri   = res + (size_t)i * n;
+  for (uint32_t k = blockIdx.x * kThreads + threadIdx.x; k < n; k += gridDim.x * kThreads) {
+    u64 last_new = mul_shoup(sub_mod(xl[k], tl[k], ql), pl.w, pl.wp, ql);
+    u64 nv       = mul_shoup(sub_mod(xi[k], ti[k], q), pi.w, pi.wp, q);
+    ri[k]        = sub_mul_const_exact(nv, last_new, wi.w, wi.wp, q);
+  }
+}
+
 // ---- key inner product (rns_poly.c:516, rns_poly_impl.c:13-160) --------------
 // One reduction per output word; two coefficients per thread (16-byte loads).
 
@@ -376,6 +412,7 @@ void launch_elementwise(EwOp op, Ptr2 res, Ptr2 a, Ptr2 b, int64_t scalar,
     EW_CASE(EW_MULADD)
     EW_CASE(EW_ADD_SCALAR)
     EW_CASE(EW_MUL_SCALAR)
+    EW_CASE(EW_MULADD_SCALAR)
   }
 #undef EW_CASE
   after_launch(c, KID_ELEMENTWISE, batch.count);
@@ -492,6 +529,17 @@ void launch_moddown_combine(const ModDownTail& args) {
   g.z    = args.polys;
   moddown_combine_kernel<<<g, kThreads, 0, c->stream>>>(args, c->d_p_inv, c->d_mod, c->N);
   after_launch(c, KID_MODDOWN_COMBINE, args.level * args.polys);
+}
+
+void launch_moddown_rescale(int64_t* res, const int64_t* x, const int64_t* t, int level) {
+  if (level < 2) return;
+  Context* c    = ctx();
+  const int last = level - 1;
+  prof_before(KID_MODDOWN_COMBINE);
+  moddown_rescale_kernel<<<grid_for(c->N, 2, last), kThreads, 0, c->stream>>>(
+      (u64*)res, (const u64*)x, (const u64*)t, last, c->d_p_inv,
+      c->d_ql_inv + (size_t)last * c->L, c->d_mod, c->N);
+  after_launch(c, KID_MODDOWN_COMBINE, last);
 }
 
 void launch_inner_product(const InnerArgs& args) {

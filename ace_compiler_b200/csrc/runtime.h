@@ -312,9 +312,31 @@ DevModulus make_dev_modulus(u64 q, uint32_t n);
 // limb.a selects the source limb of in.p[sel&1], limb.dst the result limb of
 // out.p[(sel>>2)&1]
 void launch_ntt(Ptr2 in, Ptr2 out, const LimbBatch& b, bool inverse);
+// Forward transform with the element-wise passes around it folded in (ring
+// degrees above 4096 only: ntt_can_fuse).  The strided pass reads in[a] and
+// writes limb k of `mid` (k = position in the batch), the contiguous pass reads
+// mid[k] and writes out[dst].
+//   prologue (pro_mul set): the source is the coefficient form of a dropped
+//     limb modulo q_last; the value transformed under prime i is
+//     switch_modulus(v, q_last -> q_i) * pro_mul[i]   (pro_mod[i] = q_last mod q_i)
+//   epilogue: kind 1  out = aux[b] * epi_mul[i] + t      (rescale)
+//             kind 2  out = (aux[b] - t) * epi_mul[i] (+ add[b])   (ModDown)
+//     aux / add use base p[sel bit 1]
+struct NttFuse {
+  const Twiddle* pro_mul = nullptr;
+  const u64*     pro_mod = nullptr;
+  u64            q_last  = 0;
+  int            epi_kind = 0;
+  const Twiddle* epi_mul  = nullptr;
+  Ptr2           aux{{nullptr, nullptr}};
+  Ptr2           add{{nullptr, nullptr}};
+};
+bool ntt_can_fuse();
+void launch_ntt_fused(Ptr2 in, int64_t* mid, Ptr2 out, const LimbBatch& b, const NttFuse& f);
 
-enum EwOp { EW_ADD, EW_SUB, EW_MUL, EW_MULADD, EW_ADD_SCALAR, EW_MUL_SCALAR };
-// res[dst] = a[a] op b[b]   (EW_MULADD: res[dst] += a*b; scalar ops ignore b)
+enum EwOp { EW_ADD, EW_SUB, EW_MUL, EW_MULADD, EW_ADD_SCALAR, EW_MUL_SCALAR, EW_MULADD_SCALAR };
+// res[dst] = a[a] op b[b]   (EW_MULADD: res[dst] += a*b; scalar ops ignore b;
+// EW_MULADD_SCALAR: res[dst] += a*scalar)
 void launch_elementwise(EwOp op, Ptr2 res, Ptr2 a, Ptr2 b, int64_t scalar,
                         const LimbBatch& batch);
 // res[dst] = a[a] + per_limb[k] (or * when mul) for the k-th limb of the batch;
@@ -375,6 +397,15 @@ struct ModDownTail {
   const u64* add[2];
 };
 void launch_moddown_combine(const ModDownTail& args);
+// Tail of the fused ModDown + Rescale in coefficient form (rns_poly.c:556-596):
+// x = extended polynomial (level Q limbs), t = base conversion of its special
+// limbs, both in coefficient form; with l = level - 1
+//   last  = (x_l - t_l) * P^-1 mod q_l
+//   res_i = ((x_i - t_i) * P^-1 - last) * q_l^-1 mod q_i      for i < l
+// where `last` enters the subtraction as the integer in [0, q_l), uncentred,
+// and the second step repeats the reference's 128-bit arithmetic on the
+// (possibly slightly negative) difference exactly.
+void launch_moddown_rescale(int64_t* res, const int64_t* x, const int64_t* t, int level);
 
 // Key inner product over `parts` digits for limbs m in [0, level+K):
 //   e_j = (in and m < level and m / alpha == j) ? in[m] : ext_ptr[j][m]

@@ -33,9 +33,9 @@ if [ $# -ge 2 ]; then
   build_one "$1" "$2"
   exit 0
 fi
-DATASET="${REFERENCE_ROOT:-/root/reference}/fhe-cmplr/rtlib/ant/dataset"
-if [ ! -d "$DATASET" ]; then
-  echo "no reference checkout; keeping any prebuilt programs in $OUT" >&2
+DATASET="${REFERENCE_ROOT:-}/fhe-cmplr/rtlib/ant/dataset"
+if [ -z "${REFERENCE_ROOT:-}" ] || [ ! -d "$DATASET" ]; then
+  echo "REFERENCE_ROOT names no reference checkout; keeping any prebuilt programs in $OUT" >&2
   exit 0
 fi
 for name in resnet20_cifar10 resnet32_cifar10 resnet32_cifar100 resnet44_cifar10 resnet110_cifar10; do

@@ -5,8 +5,11 @@
  * Main_graph, decrypt.  Inputs are seeded uniform[-1, 1) values; timings are
  * wall-clock around each stage with the device drained.
  *
- * usage: run_program [--shape n,c,h,w] [--seed s] [--images k] [--input name]
- *                    [--output name] [--values m] [--pin p]
+ * usage: run_program [--shape n,c,h,w] [--seed s] [--images k] [--input name]...
+ *                    [--output name] [--values m] [--pin p] [--amp a]
+ * --input may be given several times for programs with several inputs (each gets
+ * a tensor of the same shape, filled in turn from the one seeded stream); a name
+ * followed by "=0" gets zeros.  --amp a scales the values to [-a, a).
  * --pin p seeds the library's key / encryption randomness (Fhert_seed) so that two runs
  * produce the same ciphertexts and therefore the same logits, bit for bit.
  * prints one JSON line per image:
@@ -67,7 +70,9 @@ int main(int argc, char** argv) {
   uint64_t    seed     = 1;
   int         images = 1, values = 10;
   long        pin    = -1;
-  const char *in_name = "input", *out_name = "output";
+  const char *in_names[8] = {"input"}, *out_name = "output";
+  int         n_in = 0;
+  double      amp  = 1.0;
   for (int i = 1; i + 1 < argc; i += 2) {
     if (!strcmp(argv[i], "--shape"))
       sscanf(argv[i + 1], "%zu,%zu,%zu,%zu", &shape[0], &shape[1], &shape[2], &shape[3]);
@@ -75,7 +80,8 @@ int main(int argc, char** argv) {
     else if (!strcmp(argv[i], "--images")) images = atoi(argv[i + 1]);
     else if (!strcmp(argv[i], "--values")) values = atoi(argv[i + 1]);
     else if (!strcmp(argv[i], "--pin")) pin = atol(argv[i + 1]);
-    else if (!strcmp(argv[i], "--input")) in_name = argv[i + 1];
+    else if (!strcmp(argv[i], "--amp")) amp = atof(argv[i + 1]);
+    else if (!strcmp(argv[i], "--input") && n_in < 8) in_names[n_in++] = argv[i + 1];
     else if (!strcmp(argv[i], "--output")) out_name = argv[i + 1];
   }
   if (pin >= 0) {
@@ -88,15 +94,28 @@ int main(int argc, char** argv) {
   Fhert_sync();
   double setup = now_s() - t0, total = 0;
   size_t count = shape[0] * shape[1] * shape[2] * shape[3];
+  if (n_in == 0) n_in = 1;
   for (int img = 0; img < images; img++) {
-    TENSOR* t = Alloc_tensor(shape[0], shape[1], shape[2], shape[3], NULL);
-    for (size_t k = 0; k < count; k++)
-      t->_vals[k] = (double)(next_u64(&seed) >> 11) / 4503599627370496.0 - 1.0;
-    double a = now_s();
-    Prepare_input(t, in_name);
-    Fhert_sync();
-    double b = now_s();
-    Free_tensor(t);
+    double enc = 0;
+    for (int k_in = 0; k_in < n_in; k_in++) {
+      char        name[64];
+      const char* eq   = strchr(in_names[k_in], '=');
+      size_t      len  = eq ? (size_t)(eq - in_names[k_in]) : strlen(in_names[k_in]);
+      int         zero = eq != NULL && eq[1] == '0';
+      if (len >= sizeof(name)) len = sizeof(name) - 1;
+      memcpy(name, in_names[k_in], len);
+      name[len] = 0;
+      TENSOR* t = Alloc_tensor(shape[0], shape[1], shape[2], shape[3], NULL);
+      for (size_t k = 0; k < count; k++)
+        t->_vals[k] =
+            zero ? 0.0 : amp * ((double)(next_u64(&seed) >> 11) / 4503599627370496.0 - 1.0);
+      double a0 = now_s();
+      Prepare_input(t, name);
+      Fhert_sync();
+      enc += now_s() - a0;
+      Free_tensor(t);
+    }
+    double b = now_s(), a = b - enc;
     Run_main_graph();
     Fhert_sync();
     double c = now_s();

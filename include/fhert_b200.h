@@ -231,6 +231,8 @@ int64_t* Hw_modsub(int64_t* res, int64_t* a, int64_t* b, MODULUS* m, uint32_t de
 int64_t* Hw_modmul(int64_t* res, int64_t* a, int64_t* b, MODULUS* m, uint32_t degree);
 /* res += a * b */
 int64_t* Hw_modmuladd(int64_t* res, int64_t* a, int64_t* b, MODULUS* m, uint32_t degree);
+/* res += a * scalar                                      (hal.c:109) */
+int64_t* Hw_modmuladd_scalar(int64_t* res, int64_t* a, int64_t scalar, MODULUS* m, uint32_t degree);
 int64_t* Hw_modadd_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint32_t degree);
 int64_t* Hw_modmul_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint32_t degree);
 /* res[i] = val[order[i]]; `order` is what Auto_order returned */
@@ -257,6 +259,11 @@ POLY   Mod_up(POLY res, POLY poly, uint32_t part);    /* rns_poly.c:107 */
 POLY   Decomp_modup(POLY res, POLY poly, uint32_t part); /* rns_poly.c:160 */
 POLY   Mod_down(POLY res, POLY poly);                 /* rns_poly.c:260 */
 POLY   Extend(POLY res, POLY poly);                   /* rns_poly.c:483 */
+/* ModDown and Rescale fused, in coefficient form; res gets level-1 limbs in
+ * NTT form, poly is left in coefficient form          (rns_poly.c:531) */
+POLY   Mod_down_rescale(POLY res, POLY poly);
+/* prints "level not match" when the shapes differ     (rns_poly.c:606) */
+void   Chk_level(POLY res, POLY p0, POLY p1);
 /* res = sum_{j<parts} a[j]*b[j] over Q u P limbs    (rns_poly.c:516) */
 POLY   Dot_prod(POLY res, POLY a, POLY b, size_t parts);
 /* res[i] = poly[order[i]] on every limb             (rns_poly.c:1056) */

@@ -9,15 +9,15 @@
 # input, runs its Main_graph through the C-ABI, decrypts and compares with the
 # values its author expected.  Nothing is copied out of the reference tree.
 #
-# usage: oracle/build_examples.sh [reference-root]   (default /root/reference)
+# usage: oracle/build_examples.sh [reference-root]   (or REFERENCE_ROOT in the environment)
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 REPO="$(dirname "$HERE")"
-REF="${1:-/root/reference}"
+REF="${1:-${REFERENCE_ROOT:-}}"
 EG="$REF/fhe-cmplr/rtlib/ant/example"
 OUT="$HERE/_ref/examples"
-if [ ! -d "$EG" ]; then
-  echo "reference checkout not found at $REF; keeping any prebuilt $OUT" >&2
+if [ -z "$REF" ] || [ ! -d "$EG" ]; then
+  echo "no reference checkout given (argument or REFERENCE_ROOT); keeping any prebuilt $OUT" >&2
   exit 0
 fi
 LIB="$REPO/ace_compiler_b200/libFHErt_b200.so"
@@ -65,3 +65,23 @@ for name in conv_3x16x32x3 conv_16x16x32x3; do
   rm -f "$TW/$name.b200.o" "$TW/$name.ref.o"
   echo "built twins $TW/$name.{b200,ref}"
 done
+
+# bootstrap_full (N = 16384, depth 23, two inputs): a program of the EDSL front
+# end, emitted as C++ (extern "C" hooks), so both twins go through g++.
+name=bootstrap_full
+src="$DATASET/$name.inc"
+if [ -f "$src" ] && [ -f "$REFLIB" ]; then
+  g++ -O0 -w -I"$REPO/include" -include "$REPO/include/common/rtlib.h" -x c++ -c "$src" \
+      -o "$TW/$name.b200.o"
+  gcc -O2 -I"$REPO/include" -c "$DRIVER" -o "$TW/$name.drv.o"
+  g++ "$TW/$name.drv.o" "$TW/$name.b200.o" -o "$TW/$name.b200" "$LIB" -lm \
+      -Wl,-rpath,'$ORIGIN/../../../ace_compiler_b200'
+  g++ -O0 -w -fpermissive -DRTLIB_SUPPORT_LINUX -DOPENFHE_COMPAT -DNDEBUG "${RINC[@]}" \
+      -DGet_rt_data_info=Program_rt_data_info -include "$RT/include/common/rtlib.h" \
+      -x c++ -c "$src" -o "$TW/$name.ref.o"
+  gcc -O2 -std=gnu11 -DREFERENCE_RUNTIME -DRTLIB_SUPPORT_LINUX -DOPENFHE_COMPAT -DNDEBUG \
+      "${RINC[@]}" -c "$DRIVER" -o "$TW/$name.drv.ref.o"
+  g++ "$TW/$name.drv.ref.o" "$TW/$name.ref.o" -o "$TW/$name.ref" "$REFLIB" -lm -Wl,-rpath,'$ORIGIN/..'
+  rm -f "$TW/$name.b200.o" "$TW/$name.ref.o" "$TW/$name.drv.o" "$TW/$name.drv.ref.o"
+  echo "built twins $TW/$name.{b200,ref}"
+fi

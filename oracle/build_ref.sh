@@ -7,16 +7,16 @@
 # network; here they are replaced by the stand-ins in oracle/shims/.  Nothing
 # is copied out of the reference tree: sources are compiled where they lie.
 #
-# usage: oracle/build_ref.sh [reference-root]      (default /root/reference)
+# usage: oracle/build_ref.sh [reference-root]      (or REFERENCE_ROOT in the environment)
 #   env OMP=1 additionally builds libFHErt_ant_ref_omp.so (-fopenmp, the
 #   reference's BUILD_WITH_OPENMP variant).
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-REF="${1:-/root/reference}"
+REF="${1:-${REFERENCE_ROOT:-}}"
 RT="$REF/fhe-cmplr/rtlib"
 OUT="$HERE/_ref"
-if [ ! -d "$RT/ant" ]; then
-  echo "reference checkout not found at $REF; keeping any prebuilt $OUT" >&2
+if [ -z "$REF" ] || [ ! -d "$RT/ant" ]; then
+  echo "no reference checkout given (argument or REFERENCE_ROOT); keeping any prebuilt $OUT" >&2
   exit 0
 fi
 mkdir -p "$OUT/obj"

@@ -1,0 +1,175 @@
+"""Polynomial-level entry points compared bit for bit with the reference
+functions of the same name.  The reference functions are called through ctypes
+on host structs of the same layout over numpy storage (Add_poly, Sub_poly,
+Mul_poly: rns_poly.c:852-994; Dot_prod: rns_poly.c:516; Modswitch:
+rns_poly.c:406; Swk_c0 / Swk_c1: ckks/key.h:90-124; Hw_modmuladd_scalar:
+hal.c:109; Mod_down_rescale: rns_poly.c:531)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from tests import ref_runtime as rr
+
+pytestmark = pytest.mark.gpu
+
+# one context with the ResNet programs' prime sizes (51 / 46 bits: the
+# transforms then run without range correction), one with 60 / 56 bits
+PARAM_SETS = {"n8192_51_46": (8192, 6, 51, 46, 3), "n16384_60_56": (16384, 5, 60, 56, 2)}
+ROTS = (1, -2)
+
+
+@pytest.fixture(scope="module", params=list(PARAM_SETS))
+def pair(request):
+    if not rr.available():
+        pytest.skip("reference runtime not built")
+    import ace_compiler_b200 as rt
+    n, L, q0, sf, dnum = PARAM_SETS[request.param]
+    ref = rr.RefRuntime(n, L, q0, sf, dnum, rot_idxs=ROTS, seed=np.arange(16) + 21)
+    gpu = rt.Runtime(n, L, q0, sf, dnum, rot_idxs=ROTS)
+    for is_rot, idx in [(False, 0)] + [(True, r) for r in ROTS]:
+        for part in range(ref.dnum):
+            for which in (0, 1):
+                gpu.import_switch_key(is_rot, idx, part, which, ref.swk(is_rot, idx, part, which))
+    yield ref, gpu, rt
+    gpu.close()
+    rr.close_ref(ref)
+
+
+class HostPolys:
+    """An array of reference-side POLYNOMIAL structs over numpy storage: `level`
+    Q limbs followed directly by the special limbs when `extended`."""
+
+    def __init__(self, rt, n, K, datas, level, extended=False, is_ntt=True):
+        self.arr = (rt.POLYNOMIAL * len(datas))()
+        self.keep = []
+        for p, d in zip(self.arr, datas):
+            a = np.ascontiguousarray(d, np.int64)
+            self.keep.append(a)
+            p._ring_degree, p._num_primes, p._num_alloc_primes = n, level, a.shape[0]
+            p._num_primes_p = K if extended else 0
+            p._is_ntt, p._data = is_ntt, a.ctypes.data
+
+    def host(self, i=0):
+        return self.keep[i]
+
+
+def test_add_sub_mul_poly(pair):
+    ref, gpu, rt = pair
+    n, rng = gpu.N, np.random.default_rng(31)
+    for level in sorted({gpu.L, 2}):
+        a = rr.uniform_limbs(rng, gpu.primes[:level], n)
+        b = rr.uniform_limbs(rng, gpu.primes[:level], n)
+        a[:, 0] = [p - 1 for p in gpu.primes[:level]]
+        b[:, 0] = [p - 1 for p in gpu.primes[:level]]
+        a[:, 1] = 0
+        pa, pb = gpu.new_poly(level, data=a), gpu.new_poly(level, data=b)
+        for name in ("Add_poly", "Sub_poly", "Mul_poly"):
+            out = gpu.new_poly(level)
+            getattr(gpu.lib, name)(out, pa, pb)
+            h = HostPolys(rt, n, gpu.K, [a.copy(), b.copy(), np.zeros_like(a)], level)
+            f = getattr(ref.lib, name)
+            f.argtypes, f.restype = [C.c_void_p] * 3, C.c_void_p
+            f(C.byref(h.arr[2]), C.byref(h.arr[0]), C.byref(h.arr[1]))
+            assert np.array_equal(gpu.download(out), h.host(2)), (name, level)
+            gpu.free(out)
+        gpu.free(pa)
+        gpu.free(pb)
+
+
+def test_modswitch(pair):
+    ref, gpu, rt = pair
+    n, rng, level = gpu.N, np.random.default_rng(32), gpu.L
+    a = rr.uniform_limbs(rng, gpu.primes[:level], n)
+    src = gpu.new_poly(level, data=a)
+    out = gpu.new_poly(level - 1)
+    gpu.lib.Modswitch(out, src)
+    assert out.contents._num_primes == level - 1
+    assert np.array_equal(gpu.download(out), a[: level - 1])
+    gpu.lib.Modswitch(src, src)  # in place: only the level drops (rns_poly.c:406-414)
+    assert src.contents._num_primes == level - 1
+    assert np.array_equal(gpu.download(src), a[: level - 1])
+    gpu.free(src)
+    gpu.free(out)
+
+
+def test_dot_prod(pair):
+    ref, gpu, rt = pair
+    n, K, rng = gpu.N, gpu.K, np.random.default_rng(33)
+    for level in sorted({gpu.L, 2}):
+        parts = ref.num_decomp(level)
+        primes = gpu.primes[:level] + gpu.primes[gpu.L:]
+        ext = [rr.uniform_limbs(rng, primes, n) for _ in range(parts)]
+        # the second operand is a switch key: it keeps all L Q limbs, special limbs behind them
+        key = [ref.swk(True, ROTS[0], j, 0) for j in range(parts)]
+        d_ext = gpu.lib.Alloc_polys(parts, n, level, K)
+        for j in range(parts):
+            gpu.upload(C.pointer(d_ext[j]), ext[j])
+            d_ext[j]._is_ntt = True
+        views = (rt.POLYNOMIAL * gpu.dnum)()
+        gpu.lib.Swk_c0(views, gpu.dnum, True, ROTS[0])
+        out = gpu.new_poly(level, extended=True)
+        gpu.lib.Dot_prod(out, d_ext, views, parts)
+        h_ext = HostPolys(rt, n, K, ext, level, extended=True)
+        h_key = HostPolys(rt, n, K, key, gpu.L, extended=True)
+        h_out = HostPolys(rt, n, K, [np.zeros_like(ext[0])], level, extended=True)
+        f = ref.lib.Dot_prod
+        f.argtypes, f.restype = [C.c_void_p] * 3 + [C.c_uint32], C.c_void_p
+        f(C.byref(h_out.arr[0]), h_ext.arr, h_key.arr, parts)
+        assert np.array_equal(gpu.download(out), h_out.host(0)), level
+        gpu.lib.Free_polys(d_ext)
+        gpu.free(out)
+
+
+def test_swk_views_hold_the_key_material(pair):
+    ref, gpu, rt = pair
+    for is_rot, idx in ((True, ROTS[1]), (False, 0)):
+        for which, name in ((0, "Swk_c0"), (1, "Swk_c1")):
+            views = (rt.POLYNOMIAL * gpu.dnum)()
+            getattr(gpu.lib, name)(views, gpu.dnum, is_rot, idx)
+            for j in range(gpu.dnum):
+                assert views[j]._num_primes == gpu.L and views[j]._num_primes_p == gpu.K
+                assert np.array_equal(gpu.download(C.pointer(views[j])),
+                                      ref.swk(is_rot, idx, j, which)), (name, idx, j)
+
+
+def test_hw_modmuladd_scalar(pair):
+    ref, gpu, rt = pair
+    n, rng = gpu.N, np.random.default_rng(34)
+    f = ref.lib.Hw_modmuladd_scalar
+    f.argtypes, f.restype = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_uint32], C.c_void_p
+    for idx in (0, gpu.L - 1):
+        q = gpu.primes[idx]
+        acc = rr.uniform_limbs(rng, [q], n)
+        a = rr.uniform_limbs(rng, [q], n)
+        a[0, :2] = (q - 1, 0)
+        for scalar in (q - 1, 12345, 0):
+            want = acc.copy()
+            f(want.ctypes.data, a.ctypes.data, scalar, ref.lib.Ref_modulus(idx), n)
+            pa, pr = gpu.new_poly(1, data=a), gpu.new_poly(1, data=acc)
+            gpu.lib.Hw_modmuladd_scalar(gpu.limb_ptr(pr, 0), gpu.limb_ptr(pa, 0), scalar,
+                                        gpu.modulus(idx), n)
+            assert np.array_equal(gpu.download(pr), want), (idx, scalar)
+            gpu.free(pa)
+            gpu.free(pr)
+
+
+def test_mod_down_rescale(pair):
+    ref, gpu, rt = pair
+    n, K, rng = gpu.N, gpu.K, np.random.default_rng(35)
+    f = ref.lib.Mod_down_rescale
+    f.argtypes, f.restype = [C.c_void_p, C.c_void_p], C.c_void_p
+    for level in sorted({gpu.L, 2}):
+        primes = gpu.primes[:level] + gpu.primes[gpu.L:]
+        data = rr.uniform_limbs(rng, primes, n)
+        ext = gpu.new_poly(level, extended=True, data=data)
+        out = gpu.new_poly(level)
+        gpu.lib.Mod_down_rescale(out, ext)
+        h_in = HostPolys(rt, n, K, [data.copy()], level, extended=True)
+        h_out = HostPolys(rt, n, K, [np.zeros((level, n), np.int64)], level)
+        f(C.byref(h_out.arr[0]), C.byref(h_in.arr[0]))
+        assert out.contents._num_primes == h_out.arr[0]._num_primes == level - 1
+        assert bool(out.contents._is_ntt) == bool(h_out.arr[0]._is_ntt)
+        assert np.array_equal(gpu.download(out), h_out.host(0)[: level - 1]), level
+        gpu.free(ext)
+        gpu.free(out)
