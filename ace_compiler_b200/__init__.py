@@ -197,8 +197,22 @@ SIGNATURES = {
                                C.c_void_p]),
     "Fhert_shard_end": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int,
                                C.c_void_p, C.c_void_p]),
+    "Fhert_shard_end2": (None, [C.c_void_p, I64P, I64P, I64P, I64P, C.c_int32, C.c_int, I64P, I64P]),
+    "Fhert_shard_rescale_begin": (C.c_int, [I64P, I64P, C.c_size_t, C.c_int, C.c_int, I64P]),
+    "Fhert_shard_rescale_end": (None, [I64P, I64P, C.c_size_t, C.c_int, C.c_int, I64P, I64P, I64P]),
+    "Fhert_shard_tensor": (None, [I64P, I64P, I64P, I64P, C.c_size_t, C.c_int, C.c_int, I64P, I64P, I64P]),
+    "Fhert_shard_comm_id": (C.c_int, [C.c_void_p]),
+    "Fhert_shard_comm_init": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
+    "Fhert_shard_comm_destroy": (None, []),
+    "Fhert_shard_rotate": (CIPHER, [CIPHER, CIPHER, C.c_int32, C.c_int]),
+    "Fhert_shard_mul_relin": (CIPHER, [CIPHER, CIPHER, CIPHER]),
+    "Fhert_shard_rescale": (CIPHER, [CIPHER, CIPHER]),
     "Bootstrap": (CIPHER, [CIPHER, CIPHER, C.c_uint32]),
     "Bootstrap_precom": (None, [C.c_uint32]),
+    "Eval_bootstrap_ciph": (CIPHER, [CIPHER, CIPHER, C.c_uint32, C.c_uint32]),
+    "Eval_bootstrap_coeffs_to_slots_ciph": (CIPHER, [CIPHER, CIPHER, C.c_uint32]),
+    "Eval_bootstrap_eval_mod_ciph": (CIPHER, [CIPHER, CIPHER, C.c_uint32]),
+    "Eval_bootstrap_slots_to_coeffs_ciph": (CIPHER, [CIPHER, CIPHER, C.c_uint32]),
     "Fhert_bootstrap_rotations": (C.c_size_t, [C.c_uint32, C.POINTER(C.c_int32), C.c_size_t]),
     "Fhert_export_bootstrap_plain": (C.c_size_t, [C.c_uint32, C.c_int, C.c_uint32, C.c_uint32,
                                                   C.c_void_p]),

@@ -1116,6 +1116,22 @@ void approx_mod(Context* c, CIPHER ct) {
   }
 }
 
+// bootstrap.c:1795-1824: back to the message's scale, optionally dropping the imaginary part
+void finish_bootstrap(Context* c, CIPHER res, int deg) {
+  const char* clear_env  = std::getenv("RT_BTS_CLEAR_IMAG");
+  bool        clear_imag = clear_env != nullptr && std::atoi(clear_env) != 0;
+  if (clear_imag && deg >= 1) {
+    Ct conj;
+    Conjugate_ciph(conj.p(), res);
+    Add_ciph(res, res, conj.p());
+    uint64_t ratio = (uint64_t)std::pow(2., deg - 1);
+    if (ratio > 1) mul_integer(c, res, res, ratio);
+  } else {
+    mul_integer(c, res, res, (uint64_t)std::pow(2., deg));
+  }
+  while (res->_sf_degree > 1) Rescale_ciph(res, res);
+}
+
 void bootstrap_impl(Context* c, CIPHER res, CIPHER ciph, uint32_t level_after, Precom* pre) {
   const uint32_t n = c->N, m = 2 * n, slots = ciph->_slots;
   const uint32_t bts_depth =
@@ -1172,18 +1188,42 @@ void bootstrap_impl(Context* c, CIPHER res, CIPHER ciph, uint32_t level_after, P
     Add_ciph(res, res, rot.p());
   }
 
-  const char* clear_env  = std::getenv("RT_BTS_CLEAR_IMAG");
-  bool        clear_imag = clear_env != nullptr && std::atoi(clear_env) != 0;
-  if (clear_imag && deg >= 1) {
-    Ct conj;
-    Conjugate_ciph(conj.p(), res);
-    Add_ciph(res, res, conj.p());
-    uint64_t ratio = (uint64_t)std::pow(2., deg - 1);
-    if (ratio > 1) mul_integer(c, res, res, ratio);
-  } else {
-    mul_integer(c, res, res, (uint64_t)std::pow(2., deg));
+  finish_bootstrap(c, res, deg);
+}
+
+// ---------------------------------------------------------------------------
+// the bootstrap in three separately callable stages (cipher.c:585-767).  The
+// full-packed case carries the imaginary-part ciphertext from the first stage
+// to the second in a per-thread state, as the CPU runtime does.
+// ---------------------------------------------------------------------------
+
+struct StageState {
+  bool       active = false, full_packed = false;
+  uint32_t   slots  = 0;
+  bool       has_diff = false;
+  CIPHERTEXT diff{};
+};
+thread_local StageState g_stage;
+
+void clear_stage_state() {
+  if (g_stage.has_diff) Free_ciph_poly(&g_stage.diff, 1);
+  g_stage = StageState();
+}
+
+Precom* ensure_precom(Context* c, uint32_t slots) {  // cipher.c:491-517
+  auto& table = precoms(c);
+  if (table.find(slots) == table.end()) prepare_bootstrap(c, slots);
+  auto it = table.find(slots);
+  FHERT_ASSERT(it != table.end(), "Bootstrap precom is unavailable after Bootstrap_precom");
+  keygen(c, it->second);
+  return it->second;
+}
+
+void rescale_to_degree_one(CIPHER ct, CIPHER paired) {  // cipher.c:546-563 with AUTO_SCALE off
+  while (ct->_sf_degree > 1) {
+    Rescale_ciph(ct, ct);
+    if (paired != nullptr) Rescale_ciph(paired, paired);
   }
-  while (res->_sf_degree > 1) Rescale_ciph(res, res);
 }
 
 }  // namespace
@@ -1238,6 +1278,95 @@ CIPHER Bootstrap(CIPHER res, CIPHER ciph, uint32_t level_after_bts) {
 
 // ant/context/src/ckks_context.c:239-262
 void Bootstrap_precom(uint32_t num_slots) { prepare_bootstrap(ctx(), num_slots); }
+
+// ckks/src/cipher.c:565-579
+CIPHER Eval_bootstrap_ciph(CIPHER res, CIPHER ciph, uint32_t level_after_bts, uint32_t num_slots) {
+  Context* c = ctx();
+  FHERT_ASSERT(ciph->_c0_poly._num_primes > 0, "Input cipher level is exhausted");
+  ensure_precom(c, num_slots ? num_slots : ciph->_slots);
+  bootstrap_impl(c, res, ciph, level_after_bts, ensure_precom(c, ciph->_slots));
+  return res;
+}
+
+// ckks/src/cipher.c:585-665: raise to the full modulus, CoeffsToSlots, split
+// into real and imaginary parts (the latter is kept for the next stage)
+CIPHER Eval_bootstrap_coeffs_to_slots_ciph(CIPHER res, CIPHER ciph, uint32_t num_slots) {
+  Context* c = ctx();
+  clear_stage_state();
+  const uint32_t n = c->N, m = 2 * n;
+  const uint32_t slots = num_slots ? num_slots : ciph->_slots;
+  Precom*        pre   = ensure_precom(c, slots);
+  Ct raised;
+  raise_from_level0(c, raised.p(), ciph, (uint32_t)c->L);
+  raised.v._slots = slots;
+  const bool full = slots == m / 4;
+  if (!full) {
+    Ct tmp;
+    for (uint32_t j = 1; j < n / (2 * slots); j <<= 1) {
+      Rotate_ciph(tmp.p(), raised.p(), (int32_t)(j * slots));
+      Add_ciph(raised.p(), raised.p(), tmp.p());
+    }
+  }
+  linear_transform(c, res, raised.p(), pre, true);
+  Ct conj;
+  Conjugate_ciph(conj.p(), res);
+  if (full) {
+    std::memset(&g_stage.diff, 0, sizeof(g_stage.diff));
+    g_stage.has_diff = true;
+    Sub_ciph(&g_stage.diff, res, conj.p());
+    Add_ciph(res, res, conj.p());
+    mul_monomial(c, &g_stage.diff, &g_stage.diff, 3 * m / 4);
+    rescale_to_degree_one(res, &g_stage.diff);
+  } else {
+    Add_ciph(res, res, conj.p());
+    rescale_to_degree_one(res, nullptr);
+  }
+  g_stage.active      = true;
+  g_stage.full_packed = full;
+  g_stage.slots       = slots;
+  return res;
+}
+
+// ckks/src/cipher.c:667-709: the approximate modular reduction of both parts
+CIPHER Eval_bootstrap_eval_mod_ciph(CIPHER res, CIPHER ciph, uint32_t num_slots) {
+  Context*       c     = ctx();
+  const uint32_t slots = num_slots ? num_slots : ciph->_slots;
+  ensure_precom(c, slots);
+  const bool pair = g_stage.active && g_stage.full_packed && g_stage.has_diff && g_stage.slots == slots;
+  if (pair) {
+    if (res != ciph) Copy_ciph(res, ciph);
+    approx_mod(c, res);
+    approx_mod(c, &g_stage.diff);
+    mul_monomial(c, &g_stage.diff, &g_stage.diff, slots);
+    Add_ciph(res, res, &g_stage.diff);
+    Free_ciph_poly(&g_stage.diff, 1);
+    g_stage.has_diff = false;
+  } else {
+    rescale_to_degree_one(ciph, nullptr);
+    if (res != ciph) Copy_ciph(res, ciph);
+    approx_mod(c, res);
+  }
+  return res;
+}
+
+// ckks/src/cipher.c:711-767: SlotsToCoeffs and the way back to the message's scale
+CIPHER Eval_bootstrap_slots_to_coeffs_ciph(CIPHER res, CIPHER ciph, uint32_t num_slots) {
+  Context*       c     = ctx();
+  const uint32_t m     = 2 * c->N;
+  const uint32_t slots = num_slots ? num_slots : ciph->_slots;
+  Precom*        pre   = ensure_precom(c, slots);
+  linear_transform(c, res, ciph, pre, false);
+  if (slots != m / 4) {
+    Ct rot;
+    Rotate_ciph(rot.p(), res, (int32_t)slots);
+    Add_ciph(res, res, rot.p());
+  }
+  const double sf  = std::pow(2.0, (double)c->sf_bits);
+  const int    deg = (int)std::round(std::log2((double)c->primes[0] / sf));
+  finish_bootstrap(c, res, deg);
+  clear_stage_state();
+  return res;
+}
 
 size_t Fhert_bootstrap_rotations(uint32_t slots, int32_t* out, size_t cap) {
   Context* c     = ctx();

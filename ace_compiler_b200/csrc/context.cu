@@ -474,7 +474,8 @@ Context* create_context(const CKKS_PARAMS* p) {
   c->moduli.resize(total);
   c->primes_below_2_60 = std::getenv("FHERT_NO_FAST_ACC") == nullptr;
   for (int i = 0; i < total; i++) {
-    FHERT_ASSERT(c->primes[i] < (1ull << 61), "primes must be below 2^61");
+    // the lazy reductions keep up to 9q in a 64-bit word (modarith.cuh)
+    FHERT_ASSERT(c->primes[i] < 0xFFFFFFFFFFFFFFFFull / 9, "primes must be below 2^64 / 9");
     if (c->primes[i] >= (1ull << 60)) c->primes_below_2_60 = false;
     init_modulus(&c->moduli[i], c->primes[i]);
   }

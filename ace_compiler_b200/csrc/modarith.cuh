@@ -1,7 +1,8 @@
 // 64-bit modular arithmetic for RNS limbs, device side.
 //
-// All moduli are NTT-friendly primes below 2^61, so that 4q fits a signed
-// 64-bit word and lazy (Harvey) butterflies can keep values in [0, 4q).
+// All moduli are NTT-friendly primes below 2^64 / 9 (60-bit primes and a little
+// above), so that the lazy forms used here (up to 8q in the butterflies, up to
+// 9q before the last correction of a 128-bit reduction) fit a 64-bit word.
 // Residues that leave a kernel are always canonical, in [0, q): that is the
 // only property the CPU runtime's results depend on
 // (fhe-cmplr/rtlib/ant/include/util/modular.h:126-256 reduces after every
@@ -65,13 +66,26 @@ __device__ __forceinline__ u64 mul_mod(u64 a, u64 b, const DevModulus& m) {
   return r;
 }
 
+// floor(a*b / 2^64) or up to 2 less, from three 32x32 products: the exact
+// 64x64 high product costs the half-rate multiplier pipe about 16 cycles per
+// warp, this one 6.
+__device__ __forceinline__ u64 mulhi_under(u64 a, u64 b) {
+  uint32_t a0 = (uint32_t)a, a1 = (uint32_t)(a >> 32), b0 = (uint32_t)b, b1 = (uint32_t)(b >> 32);
+  uint32_t m1 = __umulhi(a1, b0), m2 = __umulhi(a0, b1);
+  u64      t;
+  asm("mul.wide.u32 %0, %1, %2;" : "=l"(t) : "r"(a1), "r"(b1));
+  return t + m1 + m2;
+}
+
 // Canonical reduction of a 128-bit value (hi:lo) < 2^127 with the two-word
 // constant mu = floor(2^128/q)  (modular.h:185-224 does the same job).  The
-// quotient estimate drops the low partial products and undershoots by at most
-// 3, so the remainder lies in [0, 5q) and 5q < 2^64.
+// quotient estimate drops the low partial products and takes the two high
+// products from three 32-bit multiplies each: it undershoots by at most 7, so
+// the remainder lies in [0, 9q), and 9q < 2^64 for every prime below 2^60.8.
 __device__ __forceinline__ u64 reduce_128(u64 hi, u64 lo, const DevModulus& m) {
-  u64 qh = hi * m.mu_hi + __umul64hi(hi, m.mu_lo) + __umul64hi(lo, m.mu_hi);
+  u64 qh = hi * m.mu_hi + mulhi_under(hi, m.mu_lo) + mulhi_under(lo, m.mu_hi);
   u64 r  = lo - qh * m.q;
+  if (r >= 8 * m.q) r -= 8 * m.q;
   if (r >= 4 * m.q) r -= 4 * m.q;
   if (r >= 2 * m.q) r -= 2 * m.q;
   if (r >= m.q) r -= m.q;

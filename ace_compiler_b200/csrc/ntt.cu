@@ -6,9 +6,9 @@ namespace fhert {
 
 namespace {
 
-// Launches that cover few limbs use narrow column tiles in the strided pass so
-// that one limb spreads over more CTAs (a Rescale transforms one or two limbs).
-constexpr int kFewLimbs = 10;
+// Column tiles of the strided pass: 4 columns (128 threads at N = 2^16, 64 CTAs
+// per limb) measured fastest at every batch size from 2 to 48 limbs; ring
+// degrees below 2^14 keep 16 columns so that a CTA has at least two warps.
 
 template <bool INV>
 void launch_dir(Ptr2 in, Ptr2 out, const LimbBatch& b) {
@@ -28,10 +28,10 @@ void launch_dir(Ptr2 in, Ptr2 out, const LimbBatch& b) {
     b2.limb[i].a   = b2.limb[i].dst;
     b2.limb[i].sel = (uint8_t)((b2.limb[i].sel & 4) | ((b2.limb[i].sel >> 2) & 1));
   }
-  const bool few = b.count <= kFewLimbs && t.logn >= 14;
+  const bool narrow_tiles = t.logn >= 14;
   if (!INV) {
     prof_before(KID_NTT_STRIDED);
-    if (few) nttk::launch_strided<false, 4>(in, out, b, t, c->stream);
+    if (narrow_tiles) nttk::launch_strided<false, 4>(in, out, b, t, c->stream);
     else nttk::launch_strided<false, 16>(in, out, b, t, c->stream);
     prof_after(KID_NTT_STRIDED, b.count);
     prof_before(KID_NTT_CONTIG);
@@ -42,7 +42,7 @@ void launch_dir(Ptr2 in, Ptr2 out, const LimbBatch& b) {
     nttk::launch_contig<true>(in, out, b, t, c->stream);
     prof_after(KID_INTT_CONTIG, b.count);
     prof_before(KID_INTT_STRIDED);
-    if (few) nttk::launch_strided<true, 4>(out, out, b2, t, c->stream);
+    if (narrow_tiles) nttk::launch_strided<true, 4>(out, out, b2, t, c->stream);
     else nttk::launch_strided<true, 16>(out, out, b2, t, c->stream);
     prof_after(KID_INTT_STRIDED, b.count);
   }
@@ -76,9 +76,9 @@ void launch_ntt_fused(Ptr2 in, int64_t* mid, Ptr2 out, const LimbBatch& b, const
     b2.limb[i].a   = (uint16_t)i;
     b2.limb[i].sel = (uint8_t)(b.limb[i].sel & 6);
   }
-  const bool few = b.count <= kFewLimbs && t.logn >= 14;
+  const bool narrow_tiles = t.logn >= 14;
   prof_before(KID_NTT_STRIDED);
-  if (few) nttk::launch_strided<false, 4>(in, ptr2(mid), b1, t, c->stream, pro);
+  if (narrow_tiles) nttk::launch_strided<false, 4>(in, ptr2(mid), b1, t, c->stream, pro);
   else nttk::launch_strided<false, 16>(in, ptr2(mid), b1, t, c->stream, pro);
   prof_after(KID_NTT_STRIDED, b.count);
   prof_before(KID_NTT_CONTIG);

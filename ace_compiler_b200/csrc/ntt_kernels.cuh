@@ -65,15 +65,6 @@ __device__ __forceinline__ Mod make_mod(u64 q) {
   return m;
 }
 
-// floor(b*p / 2^64) or up to 2 less: three 32x32 multiplies.
-__device__ __forceinline__ u64 mulhi_under(u64 b, u64 p) {
-  u32 m1 = __umulhi(hi32(b), lo32(p));
-  u32 m2 = __umulhi(lo32(b), hi32(p));
-  u64 t;
-  asm("mul.wide.u32 %0, %1, %2;" : "=l"(t) : "r"(hi32(b)), "r"(hi32(p)));
-  return t + m1 + m2;
-}
-
 // addend + b*w + h*nq  (mod 2^64): two wide and four low multiply-adds
 __device__ __forceinline__ u64 mul_chain(u64 addend, u64 b, u64 w, u64 h, u64 nq) {
   u64 t;
@@ -161,6 +152,17 @@ __device__ __forceinline__ Twiddle ld_tw(const Twiddle* p) {
   return t;
 }
 
+// Where a round takes its twiddles from.  get<L>(jb, hp) returns the twiddle of
+// local stage L with index jb + hp inside the stage (jb is the part that
+// depends on the thread, hp the unrolled butterfly-group number).
+struct TwGlobal {
+  const Twiddle* tw;   // the prime's table
+  uint32_t       node; // (1 << s0) + blk: the transform's node in the table's tree order
+  template <int L>
+  __device__ __forceinline__ Twiddle get(uint32_t jb, int hp) const {
+    return ld_tw(tw + ((size_t)node << L) + jb + hp);
+  }
+};
 // Multiple of q covering the inputs of inverse stage k (1 = first stage done,
 // inputs canonical): bound of the values after k-1 uncorrected stages is
 // 2^k q for k >= 2 and q for k = 1.
@@ -169,27 +171,26 @@ __device__ __forceinline__ u64 inv_cover(const Mod m, int k) { return k <= 1 ? m
 // One register round of R consecutive forward stages starting at local stage
 // L0 of a 2^S-point transform.  The thread holds the 8 elements
 // base | (e << LOWPOS), e = 0..7, with LOWPOS = S - L0 - R.  The twiddle of
-// local stage l for element index idx is table entry
-// (1 << (s0 + l)) + (blk << l) + (idx >> (S - l)).
-template <bool WIDE, int R, int S, int L0>
-__device__ __forceinline__ void fwd_round(u64 (&x)[8], int base, int s0, uint32_t blk,
-                                          const Twiddle* tw, const Mod m) {
-#pragma unroll
-  for (int u = 0; u < R; u++) {
-    const int      bit = R - 1 - u;
-    const int      l   = L0 + u;
-    const uint32_t tb  = (1u << (s0 + l)) + (blk << l) + ((uint32_t)base >> (S - l));
+// local stage l for element index idx is entry idx >> (S - l) of that stage
+// (table entry (1 << (s0 + l)) + (blk << l) + (idx >> (S - l))).
+template <bool WIDE, int R, int S, int L0, typename TW, int U = 0>
+__device__ __forceinline__ void fwd_round(u64 (&x)[8], int base, const TW tws, const Mod m) {
+  if constexpr (U < R) {
+    constexpr int  bit = R - 1 - U;
+    constexpr int  l   = L0 + U;
+    // the register field starts at bit S - L0 - R, so the element offset
+    // (hp << (bit+1)) shifted there and then right by S - l is hp itself
+    const uint32_t jb  = (uint32_t)base >> (S - l);
 #pragma unroll
     for (int hp = 0; hp < (8 >> (bit + 1)); hp++) {
-      // the register field starts at bit S - L0 - R, so the element offset
-      // (hp << (bit+1)) shifted there and then right by S - l is hp itself
-      Twiddle t = ld_tw(tw + tb + hp);
+      Twiddle t = tws.template get<l>(jb, hp);
 #pragma unroll
       for (int lp = 0; lp < (1 << bit); lp++) {
         int lo = (hp << (bit + 1)) | lp;
         ct_bfly<WIDE>(x[lo], x[lo | (1 << bit)], t, m);
       }
     }
+    fwd_round<WIDE, R, S, L0, TW, U + 1>(x, base, tws, m);
   }
 }
 
@@ -198,15 +199,14 @@ __device__ __forceinline__ void fwd_round(u64 (&x)[8], int base, int s0, uint32_
 // uncorrected form).  When LAST is set and the round reaches local stage 0,
 // the final butterfly applies N^-1 (fin[0] = N^-1, fin[1] = rou_inv[1]*N^-1)
 // and leaves canonical values.
-template <bool WIDE, int R, int S, int L0, int KBASE, bool LAST>
-__device__ __forceinline__ void inv_round(u64 (&x)[8], int base, int s0, uint32_t blk,
-                                          const Twiddle* tw, const Mod m, const Twiddle* fin) {
-#pragma unroll
-  for (int u = R - 1; u >= 0; u--) {
-    const int bit = R - 1 - u;
-    const int l   = L0 + u;
-    const u64 mq  = WIDE ? m.q4 : inv_cover(m, KBASE - l);
-    if (LAST && l == 0) {  // compile-time after unrolling
+template <bool WIDE, int R, int S, int L0, int KBASE, bool LAST, typename TW, int U = R - 1>
+__device__ __forceinline__ void inv_round(u64 (&x)[8], int base, const TW tws, const Mod m,
+                                          const Twiddle* fin) {
+  if constexpr (U >= 0) {
+    constexpr int bit = R - 1 - U;
+    constexpr int l   = L0 + U;
+    const u64     mq  = WIDE ? m.q4 : inv_cover(m, KBASE - l);
+    if constexpr (LAST && l == 0) {
       Twiddle n_inv = ld_tw(fin), w_n = ld_tw(fin + 1);
 #pragma unroll
       for (int hp = 0; hp < (8 >> (bit + 1)); hp++) {
@@ -221,10 +221,10 @@ __device__ __forceinline__ void inv_round(u64 (&x)[8], int base, int s0, uint32_
         }
       }
     } else {
-      const uint32_t tb = (1u << (s0 + l)) + (blk << l) + ((uint32_t)base >> (S - l));
+      const uint32_t jb = (uint32_t)base >> (S - l);
 #pragma unroll
       for (int hp = 0; hp < (8 >> (bit + 1)); hp++) {
-        Twiddle t = ld_tw(tw + tb + hp);
+        Twiddle t = tws.template get<l>(jb, hp);
 #pragma unroll
         for (int lp = 0; lp < (1 << bit); lp++) {
           int lo = (hp << (bit + 1)) | lp;
@@ -232,6 +232,7 @@ __device__ __forceinline__ void inv_round(u64 (&x)[8], int base, int s0, uint32_
         }
       }
     }
+    inv_round<WIDE, R, S, L0, KBASE, LAST, TW, U - 1>(x, base, tws, m, fin);
   }
 }
 
@@ -261,9 +262,9 @@ __device__ __forceinline__ void sts64(u32 addr, u64 v) {
 
 template <bool INV, bool WIDE, int EPI>
 __device__ __forceinline__ void contig_block(const u64* __restrict__ src, u64* __restrict__ dst,
-                                             u32 sbase, const Twiddle* __restrict__ tw,
-                                             const Mod m, u64 rq, int g, uint32_t blk, int s0,
-                                             const u64* aux, const u64* add, const Twiddle emul) {
+                                             u32 sbase, const TwGlobal tw, const Mod m, u64 rq,
+                                             int g, const u64* aux, const u64* add,
+                                             const Twiddle emul) {
   u64 x[8];
   // byte addresses inside the warp's block for the three lane patterns
   const int b1 = g;                              // elements e*32 + g
@@ -275,19 +276,19 @@ __device__ __forceinline__ void contig_block(const u64* __restrict__ src, u64* _
   if constexpr (!INV) {
 #pragma unroll
     for (int e = 0; e < 8; e++) x[e] = src[e * 32 + g];
-    fwd_round<WIDE, 3, kContigLog, 0>(x, b1, s0, blk, tw, m);
+    fwd_round<WIDE, 3, kContigLog, 0>(x, b1, tw, m);
 #pragma unroll
     for (int e = 0; e < 8; e++) sts64(a1 ^ (u32)(swz(e << 5) << 3), x[e]);
     __syncwarp();
 #pragma unroll
     for (int e = 0; e < 8; e++) x[e] = lds64(a2 ^ (u32)(swz(e << 2) << 3));
-    fwd_round<WIDE, 3, kContigLog, 3>(x, b2, s0, blk, tw, m);
+    fwd_round<WIDE, 3, kContigLog, 3>(x, b2, tw, m);
 #pragma unroll
     for (int e = 0; e < 8; e++) sts64(a2 ^ (u32)(swz(e << 2) << 3), x[e]);
     __syncwarp();
 #pragma unroll
     for (int e = 0; e < 8; e++) x[e] = lds64(a3 ^ (u32)(swz(e) << 3));
-    fwd_round<WIDE, 2, kContigLog, 6>(x, b3, s0, blk, tw, m);
+    fwd_round<WIDE, 2, kContigLog, 6>(x, b3, tw, m);
 #pragma unroll
     for (int e = 0; e < 8; e++) {
       u64 v = WIDE ? canon_4q(csub(x[e], m.q4), m) : canon_any(x[e], m, rq);
@@ -313,19 +314,19 @@ __device__ __forceinline__ void contig_block(const u64* __restrict__ src, u64* _
     __syncwarp();
 #pragma unroll
     for (int e = 0; e < 8; e++) x[e] = lds64(a3 ^ (u32)(swz(e) << 3));
-    inv_round<WIDE, 2, kContigLog, 6, 8, false>(x, b3, s0, blk, tw, m, nullptr);
+    inv_round<WIDE, 2, kContigLog, 6, 8, false>(x, b3, tw, m, nullptr);
 #pragma unroll
     for (int e = 0; e < 8; e++) sts64(a3 ^ (u32)(swz(e) << 3), x[e]);
     __syncwarp();
 #pragma unroll
     for (int e = 0; e < 8; e++) x[e] = lds64(a2 ^ (u32)(swz(e << 2) << 3));
-    inv_round<WIDE, 3, kContigLog, 3, 8, false>(x, b2, s0, blk, tw, m, nullptr);
+    inv_round<WIDE, 3, kContigLog, 3, 8, false>(x, b2, tw, m, nullptr);
 #pragma unroll
     for (int e = 0; e < 8; e++) sts64(a2 ^ (u32)(swz(e << 2) << 3), x[e]);
     __syncwarp();
 #pragma unroll
     for (int e = 0; e < 8; e++) x[e] = lds64(a1 ^ (u32)(swz(e << 5) << 3));
-    inv_round<WIDE, 3, kContigLog, 0, 8, false>(x, b1, s0, blk, tw, m, nullptr);
+    inv_round<WIDE, 3, kContigLog, 0, 8, false>(x, b1, tw, m, nullptr);
 #pragma unroll
     for (int e = 0; e < 8; e++) dst[e * 32 + g] = x[e];
   }
@@ -352,6 +353,7 @@ ntt_contig_kernel(Ptr2 in, Ptr2 out, LimbBatch batch, const Twiddle* __restrict_
   u64*             dst  = ((lr.sel & 4) ? out.p[1] : out.p[0]) + (size_t)lr.dst * n + off;
   const u32 sbase = (u32)__cvta_generic_to_shared(sm) + (u32)warp * (kContigBlock * 8);
   const int s0    = logn - kContigLog;
+
   const bool narrow = INV ? inv_narrow(dm.bits, logn) : fwd_narrow(dm.bits);
   const u64* aux  = nullptr;
   const u64* add  = nullptr;
@@ -363,10 +365,11 @@ ntt_contig_kernel(Ptr2 in, Ptr2 out, LimbBatch batch, const Twiddle* __restrict_
     if (add != nullptr) add += aoff;
     emul = ld_tw(epi.mul + lr.prime);
   }
+  const TwGlobal tws{tw, (1u << s0) + blk};
   if (narrow)
-    contig_block<INV, false, EPI>(src, dst, sbase, tw, m, dm.mu_hi, g, blk, s0, aux, add, emul);
+    contig_block<INV, false, EPI>(src, dst, sbase, tws, m, dm.mu_hi, g, aux, add, emul);
   else
-    contig_block<INV, true, EPI>(src, dst, sbase, tw, m, dm.mu_hi, g, blk, s0, aux, add, emul);
+    contig_block<INV, true, EPI>(src, dst, sbase, tws, m, dm.mu_hi, g, aux, add, emul);
 }
 
 // ---- strided columns (global stages 0 .. logN-9) ---------------------------
@@ -409,7 +412,7 @@ __device__ __forceinline__ void strided_fwd(u64 (&x)[8], const u64* __restrict__
 #pragma unroll
     for (int e = 0; e < 8; e++) x[e] = sm[(base | (e << LOWPOS)) * TC + c];
   }
-  fwd_round<WIDE, R, S1, L0>(x, base, 0, 0, tw, m);
+  fwd_round<WIDE, R, S1, L0>(x, base, TwGlobal{tw, 1u}, m);
   if constexpr (L0 + R < S1) {
     __syncthreads();
 #pragma unroll
@@ -439,7 +442,7 @@ __device__ __forceinline__ void strided_inv(u64 (&x)[8], const u64* __restrict__
     for (int e = 0; e < 8; e++) x[e] = sm[(base | (e << LOWPOS)) * TC + c];
   }
   // inverse stage count of local stage l: 8 contiguous stages came first
-  inv_round<WIDE, R, S1, L0, kContigLog + S1, true>(x, base, 0, 0, tw, m, fin);
+  inv_round<WIDE, R, S1, L0, kContigLog + S1, true>(x, base, TwGlobal{tw, 1u}, m, fin);
   if constexpr (L0 > 0) {
     __syncthreads();
 #pragma unroll

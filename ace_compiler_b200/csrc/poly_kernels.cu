@@ -130,8 +130,8 @@ __global__ void __launch_bounds__(kThreads)
 tensor_kernel(u64* __restrict__ d0, u64* __restrict__ d1, u64* __restrict__ d2,
               const u64* __restrict__ a0, const u64* __restrict__ a1,
               const u64* __restrict__ b0, const u64* __restrict__ b1,
-              const DevModulus* __restrict__ mods, uint32_t n) {
-  const DevModulus m   = mods[blockIdx.y];
+              const DevModulus* __restrict__ mods, uint32_t n, int first_prime) {
+  const DevModulus m   = mods[first_prime + blockIdx.y];
   const size_t     off = (size_t)blockIdx.y * n;
   for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads) {
     u64 x0 = a0[off + i], x1 = a1[off + i], y0 = b0[off + i], y1 = b1[off + i];
@@ -458,15 +458,21 @@ void launch_mul_const(Ptr2 res, Ptr2 val, const Twiddle* consts, const LimbBatch
   after_launch(c, KID_MUL_CONST, batch.count);
 }
 
-void launch_tensor(int64_t* d0, int64_t* d1, int64_t* d2, const int64_t* a0,
-                   const int64_t* a1, const int64_t* b0, const int64_t* b1, int level) {
-  if (level == 0) return;
+void launch_tensor_range(int64_t* d0, int64_t* d1, int64_t* d2, const int64_t* a0,
+                         const int64_t* a1, const int64_t* b0, const int64_t* b1, int first_prime,
+                         int count) {
+  if (count == 0) return;
   Context* c = ctx();
   prof_before(KID_TENSOR);
-  tensor_kernel<<<grid_for(c->N, 2, level), kThreads, 0, c->stream>>>(
+  tensor_kernel<<<grid_for(c->N, 2, count), kThreads, 0, c->stream>>>(
       (u64*)d0, (u64*)d1, (u64*)d2, (const u64*)a0, (const u64*)a1, (const u64*)b0,
-      (const u64*)b1, c->d_mod, c->N);
-  after_launch(c, KID_TENSOR, level);
+      (const u64*)b1, c->d_mod, c->N, first_prime);
+  after_launch(c, KID_TENSOR, count);
+}
+
+void launch_tensor(int64_t* d0, int64_t* d1, int64_t* d2, const int64_t* a0,
+                   const int64_t* a1, const int64_t* b0, const int64_t* b1, int level) {
+  launch_tensor_range(d0, d1, d2, a0, a1, b0, b1, 0, level);
 }
 
 void launch_rescale_lift(Ptr2 tmp, Ptr2 last, int l, const LimbBatch& batch) {

@@ -354,6 +354,11 @@ void launch_mul_const(Ptr2 res, Ptr2 val, const Twiddle* consts, const LimbBatch
 // d0 = a0*b0, d1 = a0*b1 + a1*b0, d2 = a1*b1 on `level` limbs
 void launch_tensor(int64_t* d0, int64_t* d1, int64_t* d2, const int64_t* a0,
                    const int64_t* a1, const int64_t* b0, const int64_t* b1, int level);
+// the same on `count` limbs whose pointers already point at the first of them,
+// under primes first_prime, first_prime + 1, ..
+void launch_tensor_range(int64_t* d0, int64_t* d1, int64_t* d2, const int64_t* a0,
+                         const int64_t* a1, const int64_t* b0, const int64_t* b1, int first_prime,
+                         int count);
 
 // Rescale pieces (rns_poly.c:310-404).  `last` holds, per selected base, the
 // coefficient form of the limb being dropped (prime index l) at limb.b.

@@ -1,8 +1,8 @@
 #!/usr/bin/env python
 """Benchmark of the CKKS runtime on B200.
 
-Default workload (BASELINE.json configs[0], the configuration the headline
-metric is quoted on): encrypted ResNet-20 inference, the program the ANT-ACE
+Default workload (the configuration the headline metric is quoted on):
+encrypted ResNet-20 inference, the program the ANT-ACE
 compiler emitted for resnet20_cifar10 (N = 2^16, 34 RNS limbs of 51/46 bits,
 dnum = 3, 19 bootstraps), linked unchanged against this runtime
 (ace_compiler_b200/programs/build_programs.sh builds it where the reference
@@ -13,15 +13,21 @@ compiler's format; the encoded weight plaintexts stay resident in HBM (the
 runtime's plaintext cache), so a step does not re-encode them.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                  [--workload resnet20|primitives]
+                  [--workload resnet20|primitives|bootstrap|resnet32_cifar100]
+                  [--levels 4,12,24,36]
 
 `value` is images/s over the device time of Main_graph with the encrypted
 input resident in HBM; `e2e` is images/s over the whole step from the host
 tensor to the host logits.  `--workload primitives` runs the configs[1] sweep
 at L = 36 instead (16 rotations + 16 HMult+relinearise+rescale per step), which
 is also what runs when the compiled program is not available.
-`--impl reference` times the unmodified reference CPU runtime (oracle/_ref) on
-the host cores.
+`--workload bootstrap` times one full bootstrap of a 32768-slot ciphertext at
+N = 2^16, L = 36; `--workload resnet32_cifar100` runs that compiled program the
+way the default workload runs ResNet-20.  `--impl reference` times the
+unmodified reference CPU runtime (oracle/_ref) on the host cores: samples of the
+workload's operation classes (rotations and products at three levels, weight
+encodes, per-limb vector calls, rescales, one bootstrap), extrapolated to whole
+images with the program's operation counts; also on the reference's OpenMP build.
 """
 import argparse
 import ctypes as C
@@ -50,7 +56,17 @@ WORKLOAD = ("configs[1] primitive sweep at L=36: per step 16 Rotate(k=2^0..2^15)
 # (rotations and relinearised products executed per image, from the loop nests
 # of the generated file)
 PROGRAM = "resnet20_cifar10"
-PROGRAM_SO = os.path.join(ROOT, "ace_compiler_b200", "programs", "_ref", PROGRAM + ".so")
+PROGRAM_DIR = os.path.join(ROOT, "ace_compiler_b200", "programs", "_ref")
+PROGRAM_SO = os.path.join(PROGRAM_DIR, PROGRAM + ".so")
+# other compiled programs that run through the same path: name -> (file, weight
+# entries to provide, logits, metric, workload text)
+OTHER_PROGRAMS = {
+    "resnet32_cifar100": ("resnet32_cifar100", 16000, 100,
+                          "ResNet-32 (CIFAR-100 head) CKKS inference images/s",
+                          "compiler-emitted resnet32_cifar100 program, N=2^16, 34 limbs (q0 51 "
+                          "bits, scale 46 bits), dnum=3, 31 bootstraps; one seeded uniform[-1,1] "
+                          "3x32x32 image per step; synthetic seeded weights"),
+}
 R20_LEVELS, R20_Q0, R20_SF, R20_K = 34, 51, 46, 10
 R20_ROTATIONS, R20_RELINS, R20_BOOTSTRAPS, R20_WEIGHTS = 1814, 513, 19, 6044
 R20_METRIC = "ResNet-20 CKKS inference images/s (s/image = 1/value at 1 GPU)"
@@ -283,6 +299,50 @@ def run_primitives(args):
 
     ms_rot = timed(rot_only, 2) / 2
     ms_mul = timed(mul_only, 2) / 2
+
+    # the same two primitives and the transforms at lower ciphertext levels of
+    # the same 36-limb context (digits stay 12 limbs wide: beta = ceil(l / 12))
+    per_level = {}
+    peak_gbs = peaks()[0]
+    for lv in args.levels:
+        if lv > LEVELS:
+            continue
+        ca, cb = gpu.new_ciph(ha[0][:lv], ha[1][:lv]), gpu.new_ciph(hb[0][:lv], hb[1][:lv])
+        pa = gpu.new_poly(lv, data=ha[0][:lv])
+
+        def rot_lv():
+            for r in ROTATIONS:
+                lib.Rotate_ciph(C.byref(out), C.byref(ca), r)
+
+        def mul_lv():
+            for _ in ROTATIONS:
+                lib.Mul_ciph(C.byref(prod), C.byref(ca), C.byref(cb))
+                lib.Rescale_ciph(C.byref(res), C.byref(prod))
+
+        def ntt_lv():
+            for _ in ROTATIONS:
+                lib.Conv_ntt2poly_inplace(pa)
+                lib.Conv_poly2ntt_inplace(pa)
+
+        rot_lv(); mul_lv(); ntt_lv()
+        t_rot, t_mul, t_ntt = timed(rot_lv, 2) / 2, timed(mul_lv, 2) / 2, timed(ntt_lv, 2) / 2
+        beta = -(-lv // gpu.alpha)
+        ks_b = (3 * lv + 2 * beta * (lv + gpu.K)) * LIMB_BYTES
+        k = len(ROTATIONS)
+        rot_gbs = (ks_b + 7 * lv * LIMB_BYTES) * k / (t_rot * 1e-3) / 1e9
+        mul_gbs = (7 * lv * LIMB_BYTES + ks_b + 6 * lv * LIMB_BYTES
+                   + 2 * (2 * lv - 1) * LIMB_BYTES) * k / (t_mul * 1e-3) / 1e9
+        ntt_gbs = 2 * 2 * lv * LIMB_BYTES * k / (t_ntt * 1e-3) / 1e9
+        per_level[f"L={lv}"] = {
+            "rotate_ops_s": round(k / (t_rot * 1e-3), 1), "rotate_GBs": round(rot_gbs, 1),
+            "rotate_frac": round(rot_gbs / peak_gbs, 4),
+            "hmult_relin_rescale_ops_s": round(k / (t_mul * 1e-3), 1),
+            "hmult_GBs": round(mul_gbs, 1), "hmult_frac": round(mul_gbs / peak_gbs, 4),
+            "ntt_plus_intt_limbs_s": round(2 * lv * k / (t_ntt * 1e-3), 1),
+            "ntt_GBs": round(ntt_gbs, 1), "ntt_frac": round(ntt_gbs / peak_gbs, 4)}
+        gpu.free_ciph(ca)
+        gpu.free_ciph(cb)
+        gpu.free(pa)
     with gpu.profile() as prof:
         step_resident()
     kernels = prof.kernels
@@ -337,6 +397,7 @@ def run_primitives(args):
                 "hmult_relin_rescale_ops_s": round(len(ROTATIONS) / (ms_mul * 1e-3), 2),
                 "rotate_keyswitch_alg_GBs": round(
                     ks_bytes * len(ROTATIONS) / (ms_rot * 1e-3) / 1e9, 1),
+                "per_level": per_level,
                 "kernels_one_step": {k: {"launches": v["launches"], "limbs": v["limbs"],
                                          "ms": round(v["ms"], 3)} for k, v in rows.items()},
             },
@@ -356,8 +417,50 @@ def run_primitives(args):
 # our arm, default workload: the compiled ResNet-20 program
 # ---------------------------------------------------------------------------
 
+def key_switch_roofline(lib, rt, stream, levels, rot_idx, peak):
+    """Device time of the library's whole hybrid key switch (Rotate_ciph: ModUp of
+    all digits, key inner product, ModDown, automorphism) at the given ciphertext
+    levels of the current context, against its algorithmic bytes
+    (3l + 2*beta*(l+K)) * W, beta = ceil(l / alpha)."""
+    import torch
+    n, K, alpha = lib.Degree(), lib.Get_p_cnt(), lib.Get_part_size()
+    out = {}
+    for level in levels:
+        ct, res = rt.CIPHERTEXT(), rt.CIPHERTEXT()
+        for poly in (ct._c0_poly, ct._c1_poly):
+            lib.Alloc_poly_data(C.byref(poly), n, level, 0)  # zero residues: time does not depend on values
+            poly._is_ntt = True
+        ct._slots, ct._scaling_factor, ct._sf_degree = n // 2, lib.Get_default_sc(), 1
+        for _ in range(3):
+            lib.Rotate_ciph(C.byref(res), C.byref(ct), rot_idx)
+        lib.Fhert_sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 16
+        e0.record(stream)
+        for _ in range(reps):
+            lib.Rotate_ciph(C.byref(res), C.byref(ct), rot_idx)
+        e1.record(stream)
+        lib.Fhert_sync()
+        ms = e0.elapsed_time(e1) / reps
+        beta = -(-level // alpha)
+        alg = (3 * level + 2 * beta * (level + K)) * n * 8
+        gbs = alg / (ms * 1e-3) / 1e9
+        out[f"level {level}"] = {"ms": round(ms, 4), "alg_MB": round(alg / 1e6, 1),
+                                 "GB/s": round(gbs, 1), "frac": round(gbs / peak, 4)}
+        lib.Free_ciph_poly(C.byref(ct), 1)
+        lib.Free_ciph_poly(C.byref(res), 1)
+    return out
+
+
 def run_resnet20(args):
     import torch
+
+    if args.workload in OTHER_PROGRAMS:
+        program, weight_entries, n_logits, metric, workload_text = OTHER_PROGRAMS[args.workload]
+    else:
+        program, weight_entries, n_logits = PROGRAM, R20_WEIGHTS + 56, 10
+        metric, workload_text = R20_METRIC, R20_WORKLOAD
+    program_so = os.path.join(PROGRAM_DIR, program + ".so")
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -368,14 +471,14 @@ def run_resnet20(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     from ace_compiler_b200.msgfile import write_synthetic_msg_file
-    weights = f"/tmp/fhert_{PROGRAM}_{os.getpid()}.msg"
-    write_synthetic_msg_file(weights, R20_WEIGHTS + 56, sigma=0.02, seed=7)
+    weights = f"/tmp/fhert_{program}_{os.getpid()}.msg"
+    write_synthetic_msg_file(weights, weight_entries, sigma=0.02, seed=7)
     os.environ["FHERT_DATA_FILE"] = weights
     os.environ["FHERT_PT_CACHE_MB"] = str(args.cache_mb)
     os.environ["FHERT_RT_STAT"] = "0"
     # the program's hooks (Get_context_params, Main_graph ...) must come first
     # in the global symbol scope, before the library's weak defaults
-    C.CDLL(PROGRAM_SO, mode=C.RTLD_GLOBAL)
+    C.CDLL(program_so, mode=C.RTLD_GLOBAL)
     import ace_compiler_b200 as rt
     lib = rt.load()
     libc = C.CDLL(None)
@@ -402,7 +505,7 @@ def run_resnet20(args):
             e1.record(stream)
             events.append((e0, e1))
         out = lib.Handle_output(b"output")
-        logits = [out[i] for i in range(10)]
+        logits = [out[i] for i in range(n_logits)]
         libc.free(C.cast(out, C.c_void_p))
         return logits
 
@@ -474,6 +577,9 @@ def run_resnet20(args):
               file=sys.stderr)
     stats = [C.c_size_t() for _ in range(4)]
     lib.Fhert_pt_cache_stats(*[C.byref(x) for x in stats])
+    # the library's own key switch at levels the program works at (its rotation keys
+    # are those of the program; -4096 is one of the replication rotations)
+    ks = key_switch_roofline(lib, rt, stream, R20_SAMPLE_LEVELS + (R20_LEVELS,), -4096, peaks()[0])
 
     if rank == 0:
         peak, peak_kind = peaks()
@@ -502,11 +608,10 @@ def run_resnet20(args):
         roofline = {
             "bound": "hbm", "kernel": top, "achieved": round(g["gbs"], 1), "peak": peak,
             "unit": "GB/s", "frac": round(g["gbs"] / peak, 4), "peak_kind": peak_kind,
-            # DRAM bytes per launch: read + write per limb of the forward transform
-            # pair measured by ncu at 48 limbs (profiles/ntt_forward_48limbs_N65536.md:
-            # 25.4 MB + 77.3 MB per 48-limb launch pair), scaled by the limbs per launch
-            "traffic": (round(NTT_DRAM_BYTES_PER_LIMB * g["limbs"] / max(1, g["launches"]))
+            "traffic": (round(NTT_DRAM_BYTES_PER_LIMB_CAPTURED * g["limbs"] / max(1, g["launches"]))
                         if top.startswith("ntt") else None),
+            "traffic_source": "profiler capture of the transform pair at 48 limbs, scaled by "
+                              "the limbs per launch of this run (not measured by this run)",
             "alg_bytes_per_launch": g["bytes_per_limb"] * g["limbs"] / max(1, g["launches"]),
             "avg_ms_per_launch": g["ms"] / max(1, g["launches"]),
             "share_of_image": round(g["ms"] / total_ms, 4),
@@ -514,13 +619,14 @@ def run_resnet20(args):
                            "share_of_image": round(v["ms"] / total_ms, 4)}
                        for k, v in groups.items() if k != top},
         }
+        roofline["others"]["hybrid key switch (Rotate_ciph, timed alone after the images)"] = ks
         line = {
-            "metric": R20_METRIC, "value": round(value, 4), "unit": "images/s", "n_gpus": world,
+            "metric": metric, "value": round(value, 4), "unit": "images/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_graph / args.steps, 2),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64",
             "data": "synthetic",
-            "config": {"workload": R20_WORKLOAD, "ring_degree": DEGREE, "levels": R20_LEVELS,
+            "config": {"workload": workload_text, "ring_degree": DEGREE, "levels": R20_LEVELS,
                        "dnum": DNUM, "special_primes": R20_K,
                        "s_per_image": round(ms_graph / args.steps / 1e3, 4),
                        "published_cpu_s_per_image": "1453.96 (one CPU thread, 60/56-bit primes; "
@@ -553,6 +659,9 @@ def run_resnet20(args):
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_sample("resnet20")
+            if args.workload in OTHER_PROGRAMS:
+                line["cpu_baseline"]["sample"] += (" (operation counts of the ResNet-20 program; "
+                                                   "this program executes about 1.6x as many)")
     with c_stdout_to_stderr():
         lib.Finalize_context()
     try:
@@ -565,55 +674,250 @@ def run_resnet20(args):
         print(json.dumps(line))
 
 
+
+# ---------------------------------------------------------------------------
+# our arm: one full bootstrap (CoeffToSlot / EvalMod / SlotToCoeff), 32768 slots
+# ---------------------------------------------------------------------------
+
+BTS_LEVELS = 36
+BTS_METRIC = "CKKS bootstraps/s (N=2^16, 32768 slots, 60/56-bit primes, L=36, dnum=3)"
+BTS_WORKLOAD = ("full bootstrapping of one ciphertext at N=2^16 with 32768 slots holding seeded "
+                "uniform[-1,1] values: raise, CoeffToSlot, EvalMod, SlotToCoeff (hoisted rotations)")
+
+
+def run_bootstrap(args):
+    import torch
+
+    import ace_compiler_b200 as rt
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    os.environ["RTLIB_DISABLE_BOOTSTRAP_PRECOM"] = "0"
+    t0 = time.perf_counter()
+    with c_stdout_to_stderr():
+        gpu = rt.Runtime(DEGREE, BTS_LEVELS, Q0_BITS, SF_BITS, DNUM, keygen=True,
+                         seed=np.arange(16, dtype=np.uint32) + 11 + rank)
+    lib = gpu.lib
+    lib.Fhert_sync()
+    setup_s = time.perf_counter() - t0
+    stream = torch.cuda.ExternalStream(lib.Fhert_stream(), device=torch.device("cuda", local))
+    rng = np.random.default_rng(3000 + rank)
+    values = rng.uniform(-1, 1, DEGREE // 2) + 0j
+    keep = torch.from_numpy(values.view(np.float64).copy()).pin_memory()
+    host_vals = keep.numpy().view(np.complex128)
+    level_in = 2
+
+    def fresh():
+        pt = gpu.encode(host_vals, 1, level_in)
+        ct = gpu.encrypt(pt)
+        lib.Free_plain_data(C.byref(pt))
+        return ct
+
+    def barrier():
+        lib.Fhert_sync()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    ct = fresh()
+    res = rt.CIPHERTEXT()
+    for _ in range(max(1, args.warmup)):
+        lib.Bootstrap(C.byref(res), C.byref(ct), 0)
+    barrier()
+    launches0 = lib.Fhert_kernel_launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        e0.record(stream)
+        for _ in range(args.steps):
+            lib.Bootstrap(C.byref(res), C.byref(ct), 0)
+        e1.record(stream)
+        barrier()
+    launches = lib.Fhert_kernel_launches() - launches0
+    from ace_compiler_b200 import parallel
+    ms = parallel.slowest_rank([e0.elapsed_time(e1)], device="cuda")[0]
+    value = parallel.job_throughput(args.steps, world, ms)
+    # end to end: slot values on the host -> encode + encrypt -> bootstrap -> decrypt + decode
+    barrier()
+    t0 = time.perf_counter()
+    reps = max(1, args.steps // 2)
+    for _ in range(reps):
+        c2 = fresh()
+        lib.Bootstrap(C.byref(res), C.byref(c2), 0)
+        back = gpu.decrypt_decode(res)
+        gpu.free_ciph(c2)
+    barrier()
+    e2e_ms = parallel.slowest_rank([(time.perf_counter() - t0) * 1e3], device="cuda")[0]
+    err = float(np.max(np.abs(back.real - values.real)))
+    with gpu.profile() as prof:
+        lib.Bootstrap(C.byref(res), C.byref(ct), 0)
+    out_level = res._c0_poly._num_primes
+    if rank == 0:
+        peak, peak_kind = peaks()
+        rows = {k: {"launches": v[0], "limbs": v[1], "ms": round(v[2], 3)}
+                for k, v in sorted(prof.kernels.items(), key=lambda kv: -kv[1][2])}
+        total = sum(v["ms"] for v in rows.values()) or 1.0
+
+        def fam(names):
+            sel = [rows[k] for k in names if k in rows]
+            t = sum(r["ms"] for r in sel)
+            return (2 * LIMB_BYTES * sel[0]["limbs"] / (t * 1e-3) / 1e9, t) if sel and t else (0.0, 0.0)
+        ntt_gbs, ntt_ms = fam(["ntt_strided", "ntt_contig"])
+        intt_gbs, intt_ms = fam(["intt_contig", "intt_strided"])
+        ip = rows.get("inner_product")
+        line = {
+            "metric": BTS_METRIC, "value": round(value, 4), "unit": "bootstraps/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64",
+            "data": "synthetic",
+            "config": {"workload": BTS_WORKLOAD, "ring_degree": DEGREE, "levels": BTS_LEVELS,
+                       "special_primes": gpu.K, "dnum": DNUM, "input_level": level_in,
+                       "output_level": int(out_level), "setup_s": round(setup_s, 1),
+                       "max_abs_error_of_refreshed_slots": err,
+                       "l2": "inputs_larger_than_l2 (64 rotation keys of 144 MiB and the "
+                             "transform plaintexts are streamed every bootstrap)",
+                       "parallelism": f"replicas x{world}, no communication"},
+            "e2e": {"value": round(reps * world / (e2e_ms * 1e-3), 4), "unit": "bootstraps/s",
+                    "h2d_bytes_per_step": int(values.nbytes), "d2h_bytes_per_step": int(values.nbytes)},
+            "gpu_launches": int(launches),
+            "clocks": clocks.summary(),
+            "roofline": {"bound": "hbm", "kernel": "ntt (strided+contig passes)",
+                         "achieved": round(ntt_gbs, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(ntt_gbs / peak, 4), "peak_kind": peak_kind, "traffic": None,
+                         "share_of_bootstrap": round(ntt_ms / total, 4),
+                         "others": {"intt (contig+strided passes)": {
+                             "GB/s": round(intt_gbs, 1), "frac": round(intt_gbs / peak, 4),
+                             "share_of_bootstrap": round(intt_ms / total, 4)}}},
+            "breakdown": {"device_ms_one_bootstrap_by_kernel": rows,
+                          "kernel_time_sum_ms": round(total, 2)},
+        }
+        if ip:
+            line["roofline"]["others"]["inner_product"] = {"share_of_bootstrap": round(ip["ms"] / total, 4)}
+    gpu.free_ciph(ct)
+    gpu.free_ciph(res)
+    gpu.close()
+    if world > 1:
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+
 # ---------------------------------------------------------------------------
 # reference arm / CPU baseline: the unmodified reference runtime on host cores
 # ---------------------------------------------------------------------------
 
-NTT_DRAM_BYTES_PER_LIMB = (25.4e6 + 77.3e6) / 48
+# DRAM bytes (read + write) per limb of a forward transform pair, from a profiler
+# capture of the two kernels on 48 limbs (25.2 MB strided + 33.6 MB contiguous per
+# launch pair); this run does not measure DRAM traffic itself
+NTT_DRAM_BYTES_PER_LIMB_CAPTURED = (25.2e6 + 33.6e6) / 48
 
-R20_SAMPLE_LEVEL = 10  # between the 19 limbs after a bootstrap and the 2 before the next
+# What one image of the compiled ResNet-20 program executes, by operation class
+# (static analysis of the loop nests of the generated file): the CPU figures are
+# the measured cost of each class times these counts.
+R20_SAMPLE_LEVELS = (4, 10, 18)   # the program works between 2 and 19 limbs after a bootstrap
+R20_BOOTSTRAP_LEVEL_AFTER = 16    # the program asks for 15..18
+R20_HW_LIMB_CALLS = 1_400_000     # Hw_modadd / Hw_modmul / Hw_rotate calls, one limb each
+R20_RESCALES = 3112               # polynomial rescales
 
 
-def _ref_worker(seed, steps, warmup, q, workload):
+def _ref_lib_path(omp):
+    name = "libFHErt_ant_ref_omp.so" if omp else "libFHErt_ant_ref.so"
+    return os.path.join(ROOT, "oracle", "_ref", name)
+
+
+def _ref_worker(seed, steps, warmup, q, workload, omp, bootstrap):
+    """One process = one reference context.  Times `steps` samples of the
+    workload's operation classes and sends the per-class seconds back."""
     os.dup2(2, 1)  # the library's parameter line goes to stderr
     from tests import ref_runtime as rr
+    rr.REF_LIB = _ref_lib_path(omp)
+    if bootstrap:
+        os.environ["RTLIB_DISABLE_BOOTSTRAP_PRECOM"] = "0"
     if workload == "resnet20":
-        levels, q0, sf, op_level = R20_LEVELS, R20_Q0, R20_SF, R20_SAMPLE_LEVEL
+        levels, q0, sf, op_levels = R20_LEVELS, R20_Q0, R20_SF, R20_SAMPLE_LEVELS
     else:
-        levels, q0, sf, op_level = LEVELS, Q0_BITS, SF_BITS, LEVELS
+        levels, q0, sf, op_levels = LEVELS, Q0_BITS, SF_BITS, (LEVELS,)
+    t0 = time.perf_counter()
     ref = rr.RefRuntime(DEGREE, levels, q0, sf, DNUM, rot_idxs=(1,), seed=np.arange(16) + seed)
+    setup_s = time.perf_counter() - t0
     rng = np.random.default_rng(seed)
-    c0 = rr.uniform_limbs(rng, ref.primes[:op_level], DEGREE)
-    c1 = rr.uniform_limbs(rng, ref.primes[:op_level], DEGREE)
     q.put("ready")
-    rot, mul = [], []
+    out = {"setup_s": setup_s, "rot": {}, "mul": {}, "encode": [], "hw": [], "rescale": [],
+           "bootstrap": None, "step": []}
+    if bootstrap:
+        lib = ref.lib
+        lib.Ref_bootstrap.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint32, C.c_uint32,
+                                      C.c_void_p, C.c_void_p]
+        lib.Ref_bootstrap.restype = C.c_size_t
+        vals = rng.uniform(-1, 1, DEGREE // 2) + 0j
+        c0, c1 = ref.encrypt(ref.encode(vals, 1, 2))
+        o0, o1 = np.zeros((ref.L, DEGREE), np.int64), np.zeros((ref.L, DEGREE), np.int64)
+        t = time.perf_counter()
+        lib.Ref_bootstrap(rr._p(c0), rr._p(c1), 2, DEGREE // 2, R20_BOOTSTRAP_LEVEL_AFTER,
+                          rr._p(o0), rr._p(o1))
+        out["bootstrap"] = time.perf_counter() - t
+        q.put(out)
+        return
+    cts = {lv: (rr.uniform_limbs(rng, ref.primes[:lv], DEGREE),
+                rr.uniform_limbs(rng, ref.primes[:lv], DEGREE)) for lv in op_levels}
+    vals = rng.uniform(-1, 1, DEGREE // 4) + 0j
     for it in range(warmup + steps):
-        t0 = time.perf_counter()
-        ref.rotate(c0, c1, 1)
-        t1 = time.perf_counter()
-        ref.mul_relin_rescale(c0, c1, c1, c0)
-        t2 = time.perf_counter()
-        if it >= warmup:
-            rot.append(t1 - t0)
-            mul.append(t2 - t1)
-    q.put((rot, mul))
+        rec = it >= warmup
+        s0 = time.perf_counter()
+        for lv in op_levels:
+            c0, c1 = cts[lv]
+            t0 = time.perf_counter()
+            ref.rotate(c0, c1, 1)
+            t1 = time.perf_counter()
+            ref.mul_relin_rescale(c0, c1, c1, c0)
+            t2 = time.perf_counter()
+            if rec:
+                out["rot"].setdefault(lv, []).append(t1 - t0)
+                out["mul"].setdefault(lv, []).append(t2 - t1)
+        if workload == "resnet20":
+            mid = op_levels[len(op_levels) // 2]
+            t0 = time.perf_counter()
+            ref.encode(vals, 1, mid)            # one weight plaintext (Pt_from_msg)
+            t1 = time.perf_counter()
+            a, b = cts[mid][0][0], cts[mid][1][0]
+            for _ in range(4):
+                ref.hw("Hw_modmul", a, b, 0)
+                ref.hw("Hw_modadd", a, b, 0)
+            t2 = time.perf_counter()
+            ref.rescale(cts[mid][0])
+            t3 = time.perf_counter()
+            if rec:
+                out["encode"].append(t1 - t0)
+                out["hw"].append((t2 - t1) / 8)
+                out["rescale"].append(t3 - t2)
+        if rec:
+            out["step"].append(time.perf_counter() - s0)
+    q.put(out)
 
 
-def run_reference_workers(workers, steps, warmup, workload):
-    """Each worker process owns a reference context and runs `steps` samples of
-    one Rotate plus one HMult+relin+rescale; returns the wall time of the
-    samples and the mean seconds per rotation and per product."""
-    from tests import ref_runtime as rr
-    if not rr.available():
+def run_reference_workers(workers, steps, warmup, workload, omp=False, bootstrap=False):
+    """`workers` processes, each with its own reference context, time `steps`
+    samples; with `bootstrap` one more process times one bootstrap at the
+    program's parameters meanwhile.  Returns the wall time of the samples and
+    the per-class mean seconds."""
+    if not os.path.exists(_ref_lib_path(omp)):
         return None
     ctx = mp.get_context("spawn")
     qs, ps = [], []
     for w in range(workers):
         q = ctx.Queue()
-        p = ctx.Process(target=_ref_worker, args=(100 + w, steps, warmup, q, workload))
+        p = ctx.Process(target=_ref_worker, args=(100 + w, steps, warmup, q, workload, omp, False))
         p.start()
         qs.append(q)
         ps.append(p)
+    bq = bp = None
+    if bootstrap:
+        bq = ctx.Queue()
+        bp = ctx.Process(target=_ref_worker, args=(99, 1, 0, bq, workload, omp, True))
+        bp.start()
     for q in qs:
         q.get()
     t0 = time.perf_counter()
@@ -621,60 +925,129 @@ def run_reference_workers(workers, steps, warmup, workload):
     wall = time.perf_counter() - t0
     for p in ps:
         p.join()
-    t_rot = float(np.mean([np.mean(r) for r, _ in per]))
-    t_mul = float(np.mean([np.mean(m) for _, m in per]))
-    return wall, t_rot, t_mul
+    t_bts = None
+    if bootstrap:
+        bq.get()
+        t_bts = bq.get()["bootstrap"]
+        bp.join()
+
+    def mean(key):
+        vals = [v for r in per for v in r[key]]
+        return float(np.mean(vals)) if vals else None
+
+    levels = sorted(per[0]["rot"])
+    fig = {"wall_s": wall, "workers": workers, "steps": steps,
+           "rot": {lv: float(np.mean([np.mean(r["rot"][lv]) for r in per])) for lv in levels},
+           "mul": {lv: float(np.mean([np.mean(r["mul"][lv]) for r in per])) for lv in levels},
+           "encode": mean("encode"), "hw": mean("hw"), "rescale": mean("rescale"),
+           "step": mean("step"), "bootstrap": t_bts}
+    return fig
 
 
-def _reference_figures(workers, steps, warmup, workload):
-    res = run_reference_workers(workers, steps, warmup, workload)
-    if res is None:
-        return None
-    wall, t_rot, t_mul = res
-    if workload == "resnet20":
-        # the rotations and relinearised products of one image at the sampled
-        # cost; bootstraps, encodes and element-wise work are left out, which
-        # flatters the CPU figure
-        s_image = R20_ROTATIONS * t_rot + R20_RELINS * t_mul
-        value, unit = workers / s_image, "images/s"
-        sample = (f"{workers} process(es) x {steps} sample(s) of 1 Rotate + 1 HMult+relin+rescale at "
-                  f"N=2^16, level {R20_SAMPLE_LEVEL} of {R20_LEVELS}, dnum=3 on the reference "
-                  f"library ({t_rot:.3f} s and {t_mul:.3f} s each); one image = "
-                  f"{R20_ROTATIONS} rotations + {R20_RELINS} products = {s_image:.0f} s per process, "
-                  "bootstraps / encodes / element-wise work not counted")
-        ms_step = s_image * 1e3
+def _r20_image_seconds(fig):
+    """Seconds of one ResNet-20 image on one core from the measured class costs;
+    returns (seconds, breakdown, classes left out)."""
+    rot = float(np.mean(list(fig["rot"].values())))
+    mul = float(np.mean(list(fig["mul"].values())))
+    parts = {"rotations": R20_ROTATIONS * rot, "relinearised_products": R20_RELINS * mul,
+             "weight_encodes": R20_WEIGHTS * fig["encode"],
+             "per_limb_vector_calls": R20_HW_LIMB_CALLS * fig["hw"],
+             "rescales": R20_RESCALES * fig["rescale"]}
+    missing = []
+    if fig["bootstrap"] is not None:
+        parts["bootstraps"] = R20_BOOTSTRAPS * fig["bootstrap"]
     else:
-        value, unit = 2 * steps * workers / wall, "ops/s"
-        sample = (f"{workers} process(es) x {steps} sample(s) of 1 Rotate(k=1) + 1 "
-                  f"HMult+relin+rescale at N=2^16, L=36, dnum=3 ({t_rot + t_mul:.2f} s each)")
-        ms_step = (t_rot + t_mul) * 1e3 * OPS_PER_STEP / 2
-    return value, unit, sample, ms_step
+        missing.append("bootstraps (19 per image, not timed in this short sample)")
+    return sum(parts.values()), {k: round(v, 1) for k, v in parts.items()}, missing
+
+
+def _reference_summary(fig, workload, omp):
+    workers, steps = fig["workers"], fig["steps"]
+    lib = "OpenMP build of the reference library" if omp else "reference library"
+    if workload == "resnet20":
+        s_image, parts, missing = _r20_image_seconds(fig)
+        value, unit = workers / s_image, "images/s"
+        per_level = ", ".join(f"level {lv}: rotate {fig['rot'][lv]:.3f} s, product {fig['mul'][lv]:.3f} s"
+                              for lv in sorted(fig["rot"]))
+        sample = (f"{workers} process(es) x {steps} step(s) on the {lib}; one step = 1 Rotate + 1 "
+                  f"HMult+relin+rescale at each of levels {list(sorted(fig['rot']))} of {R20_LEVELS} "
+                  f"(N=2^16, dnum=3), 1 weight encode, 8 per-limb vector calls, 1 rescale; measured: "
+                  f"{per_level}; encode {fig['encode']:.4f} s; vector call {fig['hw'] * 1e3:.3f} ms; "
+                  f"rescale {fig['rescale']:.3f} s"
+                  + (f"; one bootstrap (level_after {R20_BOOTSTRAP_LEVEL_AFTER}) {fig['bootstrap']:.1f} s"
+                     if fig["bootstrap"] is not None else "")
+                  + f"; extrapolated image = counts x class cost = {s_image:.0f} s per process {parts}"
+                  + (f"; left out: {missing}" if missing else ""))
+        extra = {"extrapolated": True, "s_per_image_one_core": round(s_image, 1),
+                 "image_breakdown_s": parts}
+    else:
+        lv = max(fig["rot"])
+        t_rot, t_mul = fig["rot"][lv], fig["mul"][lv]
+        value, unit = 2 * steps * workers / fig["wall_s"], "ops/s"
+        sample = (f"{workers} process(es) x {steps} step(s) of 1 Rotate(k=1) + 1 "
+                  f"HMult+relin+rescale at N=2^16, L={lv}, dnum=3 on the {lib} "
+                  f"({t_rot + t_mul:.2f} s each)")
+        extra = {"extrapolated": False}
+    return value, unit, sample, fig["step"] * 1e3, extra
 
 
 def cpu_baseline_sample(workload="primitives"):
-    fig = _reference_figures(1, 1, 0, workload)
+    """Rank 0, N=1 only: a bounded sample (tens of seconds of CPU work) of the
+    workload's operation classes on one host core."""
+    fig = run_reference_workers(1, 1, 0, workload)
     unit = "images/s" if workload == "resnet20" else "ops/s"
     if fig is None:
         return {"value": None, "unit": unit, "cores": 0, "kind": "reference",
                 "sample": "reference runtime library not built"}
-    value, unit, sample, _ = fig
-    return {"value": round(value, 6), "unit": unit, "cores": 1, "kind": "reference",
-            "sample": sample}
+    value, unit, sample, _, extra = _reference_summary(fig, workload, False)
+    out = {"value": round(value, 6), "unit": unit, "cores": 1, "kind": "reference",
+           "sample": sample}
+    out.update(extra)
+    return out
+
+
+def cpu_model():
+    try:
+        with open("/proc/cpuinfo") as f:
+            for ln in f:
+                if ln.startswith("model name"):
+                    return ln.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
 
 
 def run_reference(args):
     if int(os.environ.get("RANK", 0)) != 0:
         return
     cores = os.cpu_count() or 1
-    # every worker holds its own context, keys and buffers (about 1.2 GB)
-    workers = max(1, min(cores, 32))
-    fig = _reference_figures(workers, max(1, args.steps), min(1, args.warmup), args.workload)
+    r20 = args.workload == "resnet20"
+    # every worker holds its own context, keys and buffers (about 1.2 GB); with
+    # the ResNet workload one more process times a bootstrap (about 12 GB)
+    workers = max(1, min(cores - (1 if r20 else 0), 32))
+    fig = run_reference_workers(workers, max(1, args.steps), min(1, args.warmup), args.workload,
+                                bootstrap=r20)
     if fig is None:
         print(json.dumps({"impl": "reference", "unavailable":
                           "oracle/_ref/libFHErt_ant_ref.so not built on this box"}))
         return
-    value, unit, sample, ms_step = fig
-    r20 = args.workload == "resnet20"
+    value, unit, sample, ms_step, extra = _reference_summary(fig, args.workload, False)
+    baseline = {"value": round(value, 6), "unit": unit, "cores": workers, "kind": "reference",
+                "sample": sample, "cpu": cpu_model(), "nproc": cores}
+    baseline.update(extra)
+    # the reference's OpenMP build (its BUILD_WITH_OPENMP option), one process
+    # with all host threads, on the same sample
+    omp_threads = str(cores)
+    os.environ["OMP_NUM_THREADS"] = omp_threads
+    omp = run_reference_workers(1, 1, 0, args.workload, omp=True)
+    if omp is not None:
+        ov, ou, osample, _, oextra = _reference_summary(omp, args.workload, True)
+        baseline["openmp"] = {"value": round(ov, 6), "unit": ou, "OMP_NUM_THREADS": int(omp_threads),
+                              "sample": osample}
+        baseline["openmp"].update(oextra)
+    else:
+        baseline["openmp"] = {"unavailable": "oracle/_ref/libFHErt_ant_ref_omp.so not built "
+                                             "(oracle/build_ref.sh with OMP=1)"}
     line = {
         "impl": "reference", "metric": R20_METRIC if r20 else METRIC, "value": round(value, 6),
         "unit": unit, "n_gpus": int(os.environ.get("WORLD_SIZE", 1)), "steps": args.steps,
@@ -682,9 +1055,11 @@ def run_reference(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64",
         "data": "synthetic",
         "config": {"workload": R20_WORKLOAD if r20 else WORKLOAD, "ring_degree": DEGREE,
-                   "levels": R20_LEVELS if r20 else LEVELS, "dnum": DNUM},
-        "cpu_baseline": {"value": round(value, 6), "unit": unit, "cores": workers,
-                         "kind": "reference", "sample": sample},
+                   "levels": R20_LEVELS if r20 else LEVELS, "dnum": DNUM,
+                   "step": "one timed step = one sample of the workload's operation classes "
+                           "(ms_per_step is its measured wall time); value extrapolates the "
+                           "sample to whole images with the program's operation counts"},
+        "cpu_baseline": baseline,
         "e2e": {"value": round(value, 6), "unit": unit, "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
     }
@@ -700,17 +1075,28 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cache-mb", type=int, default=120000,
                     help="HBM budget of the weight-plaintext cache (resnet20 workload)")
-    ap.add_argument("--workload", default="auto", choices=["auto", "resnet20", "primitives"])
+    ap.add_argument("--workload", default="auto",
+                    choices=["auto", "resnet20", "primitives", "bootstrap"] + sorted(OTHER_PROGRAMS))
+    ap.add_argument("--levels", default="4,12,24,36",
+                    help="ciphertext levels of the per-level figures (primitives workload)")
     args = ap.parse_args()
+    args.levels = [int(x) for x in args.levels.split(",") if x]
     if args.workload == "auto":
         args.workload = "resnet20" if os.path.exists(PROGRAM_SO) else "primitives"
-    if args.workload == "resnet20" and not os.path.exists(PROGRAM_SO):
-        sys.exit(f"{PROGRAM_SO} is missing: run ace_compiler_b200/programs/build_programs.sh "
+    program_so = PROGRAM_SO
+    if args.workload in OTHER_PROGRAMS:
+        program_so = os.path.join(PROGRAM_DIR, OTHER_PROGRAMS[args.workload][0] + ".so")
+    if (args.workload == "resnet20" or args.workload in OTHER_PROGRAMS) and not os.path.exists(program_so):
+        sys.exit(f"{program_so} is missing: run ace_compiler_b200/programs/build_programs.sh "
                  "where the reference checkout is present")
     if args.impl == "reference":
+        if args.workload in OTHER_PROGRAMS or args.workload == "bootstrap":
+            args.workload = "resnet20" if args.workload in OTHER_PROGRAMS else "primitives"
         run_reference(args)
-    elif args.workload == "resnet20":
+    elif args.workload == "resnet20" or args.workload in OTHER_PROGRAMS:
         run_resnet20(args)
+    elif args.workload == "bootstrap":
+        run_bootstrap(args)
     else:
         run_primitives(args)
 

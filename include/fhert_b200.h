@@ -411,22 +411,50 @@ POLY     Swk_c0(POLY res, size_t size, bool is_rot, int32_t rot_idx);
 POLY     Swk_c1(POLY res, size_t size, bool is_rot, int32_t rot_idx);
 POLY_ARR Precomp(POLY_ARR res, size_t size, POLY input);   /* rns_poly.c:459 */
 
-/* Limb-sharded rotation for single-ciphertext latency on several GPUs (no
- * reference counterpart: the CPU runtime has no distributed mode).  Rank r of
- * `world` owns Q limbs [r*qb, (r+1)*qb) and special limbs [r*pb, (r+1)*pb),
- * qb / pb from Fhert_shard_blocks; buffers use the ordinary limb-major layout
- * with only the owned limbs valid.  The caller all-gathers gather_q (world*qb
- * limbs) between begin and mid, and gather_p0 / gather_p1 (world*pb limbs
- * each) between mid and end, with every rank's block in place; see
- * ace_compiler_b200/sharded.py.  Results equal Rotate_ciph / Conjugate_ciph on
- * the owned limbs. */
-void  Fhert_shard_blocks(size_t level, int world, int* q_block, int* p_block);
+/* Limb-sharded ciphertext operations for single-ciphertext latency on several
+ * GPUs (no reference counterpart: the CPU runtime has no distributed mode).
+ * Rank r of `world` owns Q limbs [r*qb, (r+1)*qb) and special limbs
+ * [r*pb, (r+1)*pb), qb = ceil(L / world), pb = ceil(K / world)
+ * (Fhert_shard_blocks; the owner of a limb is the same at every level).
+ * Buffers and ciphertexts use the ordinary limb-major layout with only the
+ * owned limbs valid; results equal Rotate_ciph / Conjugate_ciph / Mul_ciph /
+ * Rescale_ciph on the owned limbs.
+ *
+ * Whole operations, exchanges issued by the library as NCCL collectives on its
+ * stream (one process per GPU): rank 0 obtains a 128-byte identifier with
+ * Fhert_shard_comm_id and passes it to the other ranks by the host's own means;
+ * every rank then calls Fhert_shard_comm_init (0 = ok; world = 1 needs neither
+ * an identifier nor NCCL).  NCCL is loaded at run time (libnccl.so.2). */
+void   Fhert_shard_blocks(size_t level, int world, int* q_block, int* p_block);
+int    Fhert_shard_comm_id(void* id128);
+int    Fhert_shard_comm_init(const void* id128, int rank, int world);
+void   Fhert_shard_comm_destroy(void);
+CIPHER Fhert_shard_rotate(CIPHER res, CIPHER ciph, int32_t rot_idx, int is_conj);
+CIPHER Fhert_shard_mul_relin(CIPHER res, CIPHER a, CIPHER b);
+CIPHER Fhert_shard_rescale(CIPHER res, CIPHER ciph);
+/* The same operations as phases between which the caller runs the exchange
+ * itself (used to emulate all ranks on one GPU).  Key switch of a polynomial:
+ * all-gather gather_q (world*qb limbs) between begin and mid, gather_p0 /
+ * gather_p1 (world*pb limbs each) between mid and end, every rank's block in
+ * place.  is_conj selects the key: 0 rotation by rot_idx, 1 conjugation,
+ * 2 relinearisation (no automorphism; end2 adds add0 / add1 to the two
+ * results).  Rescale: the owner of the dropped limb fills bcast (2 limbs) in
+ * rescale_begin (returns 1 there), everyone reads it in rescale_end. */
 void* Fhert_shard_begin(const int64_t* c1, size_t level, int rank, int world, int64_t* gather_q);
 void  Fhert_shard_mid(void* state, const int64_t* c1, const int64_t* gather_q, int32_t rot_idx,
                       int is_conj, int64_t* gather_p0, int64_t* gather_p1);
 void  Fhert_shard_end(void* state, const int64_t* c0, const int64_t* gather_p0,
                       const int64_t* gather_p1, int32_t rot_idx, int is_conj, int64_t* out0,
                       int64_t* out1);
+void  Fhert_shard_end2(void* state, const int64_t* add0, const int64_t* add1,
+                       const int64_t* gather_p0, const int64_t* gather_p1, int32_t rot_idx,
+                       int is_conj, int64_t* out0, int64_t* out1);
+void  Fhert_shard_tensor(const int64_t* a0, const int64_t* a1, const int64_t* b0, const int64_t* b1,
+                         size_t level, int rank, int world, int64_t* d0, int64_t* d1, int64_t* d2);
+int   Fhert_shard_rescale_begin(const int64_t* c0, const int64_t* c1, size_t level, int rank,
+                                int world, int64_t* bcast);
+void  Fhert_shard_rescale_end(const int64_t* c0, const int64_t* c1, size_t level, int rank,
+                              int world, const int64_t* bcast, int64_t* res0, int64_t* res1);
 
 /* Bootstrapping (ant/ckks/src/cipher.c:565-583, bootstrap.c:1549-1830): raises
  * an exhausted ciphertext back to level_after_bts levels (0 = as many as the
@@ -437,6 +465,15 @@ void  Fhert_shard_end(void* state, const int64_t* c0, const int64_t* gather_p0,
  * first use (context/src/ckks_context.c:239-262). */
 CIPHER Bootstrap(CIPHER res, CIPHER ciph, uint32_t level_after_bts);
 void   Bootstrap_precom(uint32_t num_slots);
+/* the same bootstrap with an explicit slot count, and its three stages as
+ * separately callable steps: CoeffsToSlots (with the raise to the full
+ * modulus), EvalMod, SlotsToCoeffs.  The first stage leaves the imaginary-part
+ * ciphertext of a fully packed input in a per-thread state that the second
+ * stage consumes, as in the CPU runtime   (ckks/src/cipher.c:565-767) */
+CIPHER Eval_bootstrap_ciph(CIPHER res, CIPHER ciph, uint32_t level_after_bts, uint32_t num_slots);
+CIPHER Eval_bootstrap_coeffs_to_slots_ciph(CIPHER res, CIPHER ciph, uint32_t num_slots);
+CIPHER Eval_bootstrap_eval_mod_ciph(CIPHER res, CIPHER ciph, uint32_t num_slots);
+CIPHER Eval_bootstrap_slots_to_coeffs_ciph(CIPHER res, CIPHER ciph, uint32_t num_slots);
 /* rotation amounts whose keys bootstrapping at this slot count uses (ascending;
  * the conjugation key comes on top); returns how many there are */
 size_t Fhert_bootstrap_rotations(uint32_t slots, int32_t* out, size_t cap);

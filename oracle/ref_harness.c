@@ -279,6 +279,22 @@ void Ref_encode(const double* values, size_t len, uint32_t sf_degree, uint32_t l
   Free_value_list(vec);
 }
 
+//! as Ref_encode with an explicit slot count (sparse packing: slots < N/2)
+void Ref_encode_slots(const double* values, size_t len, uint32_t slots, uint32_t sf_degree,
+                      uint32_t level, int64_t* out) {
+  VALUE_LIST* vec = Alloc_value_list(DCMPLX_TYPE, len);
+  for (size_t i = 0; i < len; i++) {
+    DCMPLX_VALUE_AT(vec, i) = values[2 * i] + values[2 * i + 1] * I;
+  }
+  PLAINTEXT plain;
+  memset(&plain, 0, sizeof(plain));
+  Encode_at_level_with_sf(&plain, (CKKS_ENCODER*)Encoder(), vec, level, slots, sf_degree);
+  POLY p = Get_plain_poly(&plain);
+  memcpy(out, Get_poly_coeffs(p), Poly_level(p) * Degree() * sizeof(int64_t));
+  Free_poly_data(p);
+  Free_value_list(vec);
+}
+
 //! scalar path of Encode_double (len == 1)
 void Ref_encode_scalar(double value, uint32_t sf_degree, uint32_t level, int64_t* out) {
   PLAINTEXT plain;

@@ -23,6 +23,9 @@
 #include "prng_impl.h"
 
 extern BLAKE2_PRNG* Prng;
+#ifdef _OPENMP
+#pragma omp threadprivate(Prng) /* as the reference declares it in its OpenMP build (prng.c:13-14) */
+#endif
 BLAKE2_PRNG*        Alloc_blake2_prng();
 void                Free_prng();
 

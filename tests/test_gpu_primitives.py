@@ -15,6 +15,10 @@ PARAM_SETS = {
     "small_n1024": (1024, 5, 33, 30, 2, (1, -3)),
     "tile_n8192": (8192, 5, 60, 56, 3, (5,)),
     "tile_n65536": (65536, 7, 60, 56, 3, (1, 4096, -2)),
+    # the prime sizes of the compiled ResNet programs: the transforms of the 46-
+    # and 51-bit primes run without per-butterfly range correction
+    "chain_51_46_n65536": (65536, 6, 51, 46, 3, (1, -4096)),
+    "chain_51_46_n16384": (16384, 7, 51, 46, 2, (3,)),
 }
 
 

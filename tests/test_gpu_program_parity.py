@@ -47,3 +47,48 @@ def test_program_outputs_identical_to_reference(name, weights):
     assert got == want
     # and the same with the per-limb calls launched one by one
     assert run(ours, PROGRAMS[name], weights, {"FHERT_EAGER_HW": "1"}) == want
+
+
+def splitmix_uniform(seed, count, amp):
+    """The driver's input stream (run_program.c): splitmix64, top 53 bits, [-amp, amp)."""
+    out, state, mask = [], seed, (1 << 64) - 1
+    for _ in range(count):
+        state = (state + 0x9E3779B97F4A7C15) & mask
+        z = state
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & mask
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & mask
+        z ^= z >> 31
+        out.append(amp * ((z >> 11) / 4503599627370496.0 - 1.0))
+    return out
+
+
+@pytest.mark.gpu
+def test_bootstrap_full_program_identical_to_reference(tmp_path):
+    """dataset/bootstrap_full (N = 16384, depth 23, two inputs, written out in
+    polynomial-level calls): the outputs equal the reference runtime's bit for
+    bit and approximate sin(8x) of the first input within the tolerance of the
+    program's own driver (bootstrap_full.main.inc:17-35, 1e-2)."""
+    import math
+    from ace_compiler_b200.msgfile import write_synthetic_msg_file
+    ours, ref = os.path.join(TWINS, "bootstrap_full.b200"), os.path.join(TWINS, "bootstrap_full.ref")
+    if not (os.path.exists(ours) and os.path.exists(ref)):
+        pytest.skip("twin binaries not built (oracle/build_examples.sh)")
+    weights = str(tmp_path / "unused.msg")  # the program reads no weights; the file must exist
+    write_synthetic_msg_file(weights, 2, entry_floats=64, distinct=2, sigma=0.05, seed=1)
+    args = ["--pin", "9", "--seed", "5", "--shape", "1,1,1,8", "--input", "p0", "--input", "p1=0",
+            "--amp", "0.8", "--values", "8"]
+
+    def go(exe, extra=None):
+        env = dict(os.environ, FHERT_DATA_FILE=weights, FHERT_RT_STAT="0")
+        env.update(extra or {})
+        out = subprocess.run([exe] + args, capture_output=True, text=True, timeout=900, env=env)
+        assert out.returncode == 0, (out.stdout + out.stderr)[-2000:]
+        return json.loads([ln for ln in out.stdout.splitlines() if ln.startswith('{"image"')][0])["logits"]
+
+    want = go(ref)
+    got = go(ours)
+    assert got == want
+    assert go(ours, {"FHERT_EAGER_HW": "1"}) == want
+    x = splitmix_uniform(5, 8, 0.8)
+    for v, xi in zip(got, x):
+        assert abs(v - math.sin(8 * xi)) < 1e-2

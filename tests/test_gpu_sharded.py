@@ -1,6 +1,8 @@
-"""Limb-sharded rotation: the per-rank phases run for every rank on one GPU
-(device copies in place of the all-gathers) and, where two GPUs are visible,
-as two NCCL ranks; the assembled result equals Rotate_ciph / the reference."""
+"""Limb-sharded rotation, multiplication with relinearisation and rescale:
+the per-rank phases run for every rank on one GPU (device copies in place of
+the collectives) and, where two GPUs are visible, as two ranks whose exchanges
+the library issues itself through NCCL; the assembled results equal the
+reference runtime's."""
 import ctypes as C
 import os
 import socket
@@ -44,6 +46,19 @@ def test_all_ranks_on_one_gpu(pair, world):
             assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1]), (world, level, rot)
 
 
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8])
+def test_mul_relin_and_rescale_all_ranks_on_one_gpu(pair, world):
+    from ace_compiler_b200 import sharded
+    ref, gpu = pair
+    rng = np.random.default_rng(60 + world)
+    for level in (L, 6, 2):
+        a0, a1, b0, b1 = (rr.uniform_limbs(rng, gpu.primes[:level], N) for _ in range(4))
+        p0, p1 = sharded.emulate_mul_relin(gpu, a0, a1, b0, b1, world)
+        r0, r1 = sharded.emulate_rescale(gpu, p0, p1, world)
+        w0, w1 = ref.mul_relin_rescale(a0, a1, b0, b1)
+        assert np.array_equal(r0, w0) and np.array_equal(r1, w1), (world, level)
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -83,6 +98,25 @@ def _nccl_rank(rank, world, port, q):
     got = gpu.ciph_to_host(out)
     ok = all(np.array_equal(got[0][i], want[0][i]) and np.array_equal(got[1][i], want[1][i])
              for i in mine)
+    # the same rotation, then a product and a rescale, with the exchanges inside the library
+    ops = sharded.ShardedOps(gpu, rank, world)
+    res = rt.CIPHERTEXT()
+    ops.rotate(res, ct, ROTS[0])
+    got = gpu.ciph_to_host(res)
+    ok = ok and all(np.array_equal(got[0][i], want[0][i]) and np.array_equal(got[1][i], want[1][i])
+                    for i in mine)
+    prod_whole, resc_whole = rt.CIPHERTEXT(), rt.CIPHERTEXT()
+    gpu.lib.Mul_ciph(C.byref(prod_whole), C.byref(full), C.byref(whole))
+    gpu.lib.Rescale_ciph(C.byref(resc_whole), C.byref(prod_whole))
+    want2 = gpu.ciph_to_host(resc_whole)
+    prod, resc = rt.CIPHERTEXT(), rt.CIPHERTEXT()
+    ops.mul_relin(prod, ct, res)
+    ops.rescale(resc, prod)
+    got2 = gpu.ciph_to_host(resc)
+    mine2 = [i for i in mine if i < L - 1]
+    ok = ok and all(np.array_equal(got2[0][i], want2[0][i]) and np.array_equal(got2[1][i], want2[1][i])
+                    for i in mine2)
+    ops.close()
     dist.barrier()
     q.put((rank, ok, mine))
     gpu.close()
