@@ -19,7 +19,7 @@ def _stale():
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if not f.startswith("probe_")]
     deps.append(os.path.join(HERE, "..", "include", "fhert_b200.h"))
     return any(os.path.getmtime(d) > t for d in deps)
 
@@ -50,5 +50,16 @@ def build(force=False, verbose=False):
     return LIB
 
 
+def build_probes():
+    """The stand-alone pipe / butterfly probe (csrc/probe_butterfly.cu)."""
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    out = os.path.join(HERE, "probe_butterfly.bin")
+    subprocess.check_call([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3",
+                           os.path.join(CSRC, "probe_butterfly.cu"), "-o", out])
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--probes" in sys.argv:
+        print(build_probes())

@@ -41,10 +41,10 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     n, L = args.degree, args.levels
     saved = os.dup(1)
-    os.dup2(2, 1)  # the library prints its parameter line with C stdio
+    os.dup2(2, 1)  # the library and NCCL print their greeting lines with C stdio
+    if world > 1:
+        dist.barrier()
     gpu = rt.Runtime(n, L, 60, 56, 3, rot_idxs=(1,))
-    C.CDLL(None).fflush(None)
-    os.dup2(saved, 1)
     lib = gpu.lib
     rng = np.random.default_rng(5)  # the same keys and ciphertext on every rank
     for is_rot, idx in ((False, 0), (True, 1)):
@@ -56,6 +56,8 @@ def main():
     c1 = np.stack([rng.integers(0, p, n, dtype=np.int64) for p in gpu.primes[:L]])
     ct = gpu.new_ciph(c0, c1)
     ops = sharded.ShardedOps(gpu, rank, world)
+    C.CDLL(None).fflush(None)
+    os.dup2(saved, 1)
     stream = torch.cuda.ExternalStream(lib.Fhert_stream(), device=torch.device("cuda", local))
     rot, prod, resc = rt.CIPHERTEXT(), rt.CIPHERTEXT(), rt.CIPHERTEXT()
 

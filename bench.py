@@ -205,6 +205,8 @@ def run_primitives(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        with c_stdout_to_stderr():  # NCCL prints its version line when the communicator is made
+            dist.barrier()
 
     with c_stdout_to_stderr():
         gpu = rt.Runtime(DEGREE, LEVELS, Q0_BITS, SF_BITS, DNUM, rot_idxs=ROTATIONS)
@@ -469,6 +471,8 @@ def run_resnet20(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        with c_stdout_to_stderr():  # NCCL prints its version line when the communicator is made
+            dist.barrier()
 
     from ace_compiler_b200.msgfile import write_synthetic_msg_file
     weights = f"/tmp/fhert_{program}_{os.getpid()}.msg"
@@ -697,6 +701,8 @@ def run_bootstrap(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        with c_stdout_to_stderr():  # NCCL prints its version line when the communicator is made
+            dist.barrier()
     os.environ["RTLIB_DISABLE_BOOTSTRAP_PRECOM"] = "0"
     t0 = time.perf_counter()
     with c_stdout_to_stderr():
