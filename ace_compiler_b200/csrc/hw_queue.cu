@@ -465,6 +465,13 @@ bool hw_record(Context* c, HwKind kind, int64_t* res, const int64_t* a, const in
     depend(u.read_level, u.read_chain, false);
     depend(u.write_level, u.write_chain, false);
   }
+  // a write that lands in the kept digits themselves (a result limb of Decomp_modup
+  // is an alias of them until something overwrites it): what is kept no longer
+  // equals the raised polynomial, later Decomp_modup calls must raise afresh
+  if (c->raised.valid && out >= reinterpret_cast<u64*>(c->raised.digits) &&
+      out < reinterpret_cast<u64*>(c->raised.digits) +
+                (size_t)c->raised.parts * (c->raised.level + c->K) * c->N)
+    c->raised.valid = false;
   int level = std::max(hard + 1, soft_level), chain;
   if (soft_level == level && !soft_clash) {
     chain = soft_chain;  // continues the chain of what it depends on

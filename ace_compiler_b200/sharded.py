@@ -91,6 +91,9 @@ class ShardedRotator:
         self.gq = torch.zeros((world * self.qb, n), dtype=torch.int64, device=dev)
         self.gp = [torch.zeros((world * self.pb, n), dtype=torch.int64, device=dev) for _ in (0, 1)]
         self.stream = torch.cuda.ExternalStream(self.lib.Fhert_stream(), device=dev)
+        # the zero fills above ran on torch's current stream; the library stream does
+        # not order itself against that one
+        self.stream.wait_stream(torch.cuda.current_stream())
 
     def _gather(self, buf, block):
         import torch.distributed as dist

@@ -286,3 +286,28 @@ def test_kept_digits_follow_the_program(gpu):
     assert np.array_equal(got, gpu.download(ref))
     for p in list(alone.values()) + [src, src2, ext, acc, ref]:
         gpu.free(p)
+
+
+def test_write_into_a_handed_out_digit_does_not_spoil_later_digits(gpu):
+    """A result limb of Decomp_modup is an alias of the digits the library keeps; a
+    recorded in-place write to that limb must not change what a second
+    Decomp_modup of the same, unchanged polynomial returns."""
+    lib = gpu.lib
+    rng = np.random.default_rng(44)
+    level = L
+    data = np.stack([rng.integers(0, p, N, dtype=np.int64) for p in gpu.primes[:level]])
+    src = gpu.new_poly(level, data=data)
+    fresh = gpu.new_poly(level, extended=True)
+    lib.Decomp_modup(fresh, src, 0)
+    want = gpu.download(fresh)          # (the download drains the recording: kept digits go)
+    ext, ext2 = gpu.new_poly(level, extended=True), gpu.new_poly(level, extended=True)
+    lib.Decomp_modup(ext, src, 0)
+    limb = level - 1                    # a limb outside digit 0: a converted one
+    lib.Hw_modadd_scalar(gpu.limb_ptr(ext, limb), gpu.limb_ptr(ext, limb), 7, gpu.modulus(limb), N)
+    lib.Decomp_modup(ext2, src, 0)
+    assert np.array_equal(gpu.download(ext2), want)
+    changed = want.copy()
+    changed[limb] = (changed[limb] + 7) % gpu.primes[limb]
+    assert np.array_equal(gpu.download(ext), changed)
+    for p in (src, fresh, ext, ext2):
+        gpu.free(p)
