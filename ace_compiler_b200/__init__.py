@@ -69,6 +69,13 @@ class MODULUS(C.Structure):
 
 
 POLY = C.POINTER(POLYNOMIAL)
+
+
+class L_POLY(C.Structure):  # one RNS limb (ant/include/lpoly/poly.h:18-24)
+    _fields_ = [("_ring_degree", C.c_uint32), ("_is_ntt", C.c_bool), ("_data", C.c_void_p)]
+
+
+LPOLY = C.POINTER(L_POLY)
 CIPHER = C.POINTER(CIPHERTEXT)
 CIPHER3 = C.POINTER(CIPHERTEXT3)
 PLAIN = C.POINTER(PLAINTEXT)
@@ -112,6 +119,24 @@ SIGNATURES = {
     "Hw_modmul": (C.c_void_p, [I64P, I64P, I64P, MODP, C.c_uint32]),
     "Hw_modmuladd": (C.c_void_p, [I64P, I64P, I64P, MODP, C.c_uint32]),
     "Hw_modmuladd_scalar": (C.c_void_p, [I64P, I64P, C.c_int64, MODP, C.c_uint32]),
+    "Hw_modsub_scalar": (C.c_void_p, [I64P, I64P, C.c_int64, MODP, C.c_uint32]),
+    "Alloc_lpoly_data": (None, [LPOLY, C.c_uint32]),
+    "Init_lpoly_data": (None, [LPOLY, C.c_uint32, I64P]),
+    "Free_lpoly_data": (None, [LPOLY]),
+    "Alloc_lpoly": (LPOLY, [C.c_uint32]),
+    "Free_lpoly": (None, [LPOLY]),
+    "Zero_lpoly": (None, [LPOLY]),
+    "Copy_lpoly": (None, [LPOLY, L_POLY]),
+    "Add_lpoly": (LPOLY, [LPOLY, L_POLY, L_POLY, MODP]),
+    "Add_scalar": (LPOLY, [LPOLY, L_POLY, C.c_int64, MODP]),
+    "Sub_lpoly": (LPOLY, [LPOLY, L_POLY, L_POLY, MODP]),
+    "Sub_scalar": (LPOLY, [LPOLY, L_POLY, C.c_int64, MODP]),
+    "Mul_lpoly": (LPOLY, [LPOLY, L_POLY, L_POLY, MODP]),
+    "Mul_scalar": (LPOLY, [LPOLY, L_POLY, C.c_int64, MODP]),
+    "Mac_lpoly": (LPOLY, [LPOLY, L_POLY, L_POLY, MODP]),
+    "Mac_scalar": (LPOLY, [LPOLY, L_POLY, C.c_int64, MODP]),
+    "Ntt": (None, [LPOLY, L_POLY, C.c_size_t]),
+    "Intt": (None, [LPOLY, L_POLY, C.c_size_t]),
     "Hw_modadd_scalar": (C.c_void_p, [I64P, I64P, C.c_int64, MODP, C.c_uint32]),
     "Hw_modmul_scalar": (C.c_void_p, [I64P, I64P, C.c_int64, MODP, C.c_uint32]),
     "Hw_rotate": (C.c_void_p, [I64P, I64P, I64P, MODP, C.c_uint32]),

@@ -342,6 +342,10 @@ int64_t* Hw_modadd_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint3
 int64_t* Hw_modmul_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint32_t degree) {
   return hw_binary(EW_MUL_SCALAR, res, a, a, s, m, degree);
 }
+int64_t* Hw_modsub_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint32_t degree) {
+  // hal.c:56-66: a - s = a + (-s); the scalar is reduced into [0, q) when recorded
+  return hw_binary(EW_ADD_SCALAR, res, a, a, -s, m, degree);
+}
 int64_t* Hw_modmuladd_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint32_t degree) {
   // hal.c:109-121; no compiled program emits it, so it is launched at once
   Context* c = ctx();

@@ -8,6 +8,16 @@
 // pt_mgr.c:179-214).  Every call site asks for the same (entry, offset, len,
 // scale, level) each time it runs, so an optional device-resident cache keeps
 // the encoded limbs in HBM and hands out borrowed views.
+//
+// A file of the other entry type, DE_PLAINTEXT, holds plaintexts the offline
+// encoder of the CPU runtime already encoded (one PLAINTEXT_BUFFER per entry:
+// fhe-cmplr/include/fhe/core/rt_encode_api.h:22-27, written by
+// Encode_plain_buffer, rtlib/ant/ckks/src/plain.c:196-217; read by
+// pt_mgr.c:128-159): 8 bytes "ANTPLAIN", version, size, then the host
+// PLAINTEXT struct with a null data pointer followed by level * N residues in
+// NTT form.  Such an entry is uploaded the first time it is asked for and stays
+// on the device; the caller's struct is filled with a borrowed view, which is
+// what Free_data leaves alone for this file type (pt_mgr.c:179-183).
 #include <cstring>
 #include <ctime>
 #include <map>
@@ -78,9 +88,63 @@ const float* entry_floats(uint32_t index, size_t ofst, size_t len) {
   return reinterpret_cast<const float*>(g_file.payload.data() + at) + ofst;
 }
 
+struct PlainBufferHead {  // rt_encode_api.h:22-27
+  char     magic[8];
+  uint32_t version;
+  uint32_t size;
+};
+
+// entry `index` of a DE_PLAINTEXT file as a device-resident plaintext
+void* plain_from_encoded_entry(void* pt, uint32_t index, uint32_t level) {
+  PLAIN plain = (PLAIN)pt;
+  FHERT_ASSERT(index < g_file.hdr.ent_count, "index out of entry range");
+  CacheKey key{index, 0, 0, 0, 0};
+  auto     it = g_cache.entries.find(key);
+  if (it == g_cache.entries.end()) {
+    const LutEntry& e = g_file.lut[index];
+    FHERT_ASSERT(e.ent_ofst >= kPage && e.ent_ofst - kPage + e.size <= g_file.payload.size(),
+                 "entry outside the file");
+    const char* at = g_file.payload.data() + (e.ent_ofst - kPage);
+    PlainBufferHead head;
+    std::memcpy(&head, at, sizeof(head));
+    FHERT_ASSERT(std::memcmp(head.magic, "ANTPLAIN", 8) == 0 &&
+                     sizeof(head) + head.size <= e.size && head.size >= sizeof(PLAINTEXT),
+                 "entry %u is not an encoded plaintext", index);
+    PLAINTEXT fresh;
+    std::memcpy(&fresh, at + sizeof(head), sizeof(PLAINTEXT));
+    Context*     c      = ctx();
+    const size_t limbs  = fresh._poly._num_primes + fresh._poly._num_primes_p;
+    const size_t words  = limbs * (size_t)fresh._poly._ring_degree;
+    FHERT_ASSERT(fresh._poly._ring_degree == c->N && limbs > 0 &&
+                     sizeof(PLAINTEXT) + words * sizeof(int64_t) <= head.size,
+                 "encoded plaintext %u does not fit this context", index);
+    fresh._poly._num_alloc_primes = limbs;
+    fresh._poly._data             = nullptr;
+    CUDA_CHECK(dev_alloc(&fresh._poly._data, words * sizeof(int64_t), c->stream));
+    CUDA_CHECK(counted_copy(fresh._poly._data, at + sizeof(head) + sizeof(PLAINTEXT),
+                            words * sizeof(int64_t), cudaMemcpyHostToDevice, c->stream));
+    g_cache.bytes += words * sizeof(int64_t);
+    g_cache.misses++;
+    it = g_cache.entries.emplace(key, fresh).first;
+    g_cache.owned.insert(fresh._poly._data);
+  } else {
+    g_cache.hits++;
+  }
+  FHERT_ASSERT(level == 0 || level == it->second._poly._num_primes,
+               "plaintext %u was encoded at level %zu, asked for at level %u", index,
+               it->second._poly._num_primes, level);
+  if (plain->_poly._data && !cache_owns(plain->_poly._data)) Free_poly_data(&plain->_poly);
+  *plain = it->second;
+  return pt;
+}
+
 void* plain_from_entry(void* pt, uint32_t index, size_t ofst, size_t len, uint32_t scale,
                        uint32_t level) {
   PLAIN        plain = (PLAIN)pt;
+  if (g_file.open && g_file.hdr.ent_type == DE_PLAINTEXT) {
+    FHERT_ASSERT(ofst == 0, "bad entry type");  // pt_mgr.c:204
+    return plain_from_encoded_entry(pt, index, level);
+  }
   const float* data  = entry_floats(index, ofst, len);
   if (g_cache.budget == 0 || g_cache.bypass) {
     if (plain->_poly._data && cache_owns(plain->_poly._data)) {  // a borrowed view: drop it
@@ -120,7 +184,10 @@ void* plain_from_entry(void* pt, uint32_t index, size_t ofst, size_t len, uint32
 namespace fhert {
 // programs of the older generation release plaintexts with Free_poly_data;
 // limbs lent out by the cache must survive that
-bool pt_cache_owns(const void* data) { return g_cache.budget != 0 && cache_owns(data); }
+bool pt_cache_owns(const void* data) {
+  return (g_cache.budget != 0 || (g_file.open && g_file.hdr.ent_type == DE_PLAINTEXT)) &&
+         cache_owns(data);
+}
 }  // namespace fhert
 
 extern "C" {
@@ -143,9 +210,6 @@ bool Pt_mgr_init(const char* fname) {
   }
   std::fclose(f);
   FHERT_ASSERT(ok, "failed to read rt data file %s", fname);
-  FHERT_ASSERT(df.hdr.ent_type != DE_PLAINTEXT,
-               "data files of pre-encoded CPU plaintexts are not supported; use a message file "
-               "and the device plaintext cache (FHERT_PT_CACHE_MB)");
   df.open = true;
   g_file  = std::move(df);
   const char* mb = std::getenv("FHERT_PT_CACHE_MB");
@@ -181,7 +245,7 @@ void* Pt_from_msg_ofst(void* pt, uint32_t index, size_t ofst, size_t len, uint32
 void Free_data(void* poly) {
   POLY p = (POLY)poly;
   if (!g_file.open || p->_data == nullptr) return;
-  if (g_cache.budget != 0 && cache_owns(p->_data)) {
+  if (cache_owns(p->_data)) {
     p->_data             = nullptr;
     p->_num_alloc_primes = 0;
     return;

@@ -12,6 +12,7 @@ import numpy as np
 PAGE = 4096
 ALIGN_LOG2 = 5
 DE_MSG_F32 = 0
+DE_PLAINTEXT = 2
 
 
 def write_msg_file(path, entries, model=b"synthetic", uuid=b"0" * 36):
@@ -34,6 +35,32 @@ def write_msg_file(path, entries, model=b"synthetic", uuid=b"0" * 36):
     header = struct.pack("<8sIHBBQQqq48s40s", b"!ANTFHE\0", 0, 0, DE_MSG_F32, ALIGN_LOG2,
                          len(entries), lut_ofst, 0, 0, model, uuid)
     assert len(header) == 136
+    with open(path, "wb") as f:
+        f.write(header + b"\0" * (PAGE - len(header)))
+        f.write(payload)
+        f.write(lut)
+    return lut_ofst
+
+
+def write_plaintext_file(path, buffers, model=b"synthetic", uuid=b"0" * 36):
+    """A data file of pre-encoded plaintexts (entry type DE_PLAINTEXT): buffers is
+    a list of (name, bytes, scale_degree, level) where bytes is one
+    PLAINTEXT_BUFFER as the reference's Encode_plain_buffer returns it
+    (fhe-cmplr/include/fhe/core/rt_encode_api.h:22-27)."""
+    payload = bytearray()
+    lut = bytearray()
+    for index, (name, data, scale, level) in enumerate(buffers):
+        pad = (-len(payload)) % (1 << ALIGN_LOG2)
+        payload += b"\0" * pad
+        offset = PAGE + len(payload)
+        payload += data
+        packed = (scale & 0xFF) | ((level & 0xFF) << 8) | (offset << 16)
+        lut += struct.pack("<16sIIQ", name.encode()[:15], index, len(data), packed)
+    pad = (-len(payload)) % (1 << ALIGN_LOG2)
+    payload += b"\0" * pad
+    lut_ofst = PAGE + len(payload)
+    header = struct.pack("<8sIHBBQQqq48s40s", b"!ANTFHE\0", 0, 0, DE_PLAINTEXT, ALIGN_LOG2,
+                         len(buffers), lut_ofst, 0, 0, model, uuid)
     with open(path, "wb") as f:
         f.write(header + b"\0" * (PAGE - len(header)))
         f.write(payload)

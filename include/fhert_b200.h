@@ -235,6 +235,8 @@ int64_t* Hw_modmuladd(int64_t* res, int64_t* a, int64_t* b, MODULUS* m, uint32_t
 int64_t* Hw_modmuladd_scalar(int64_t* res, int64_t* a, int64_t scalar, MODULUS* m, uint32_t degree);
 int64_t* Hw_modadd_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint32_t degree);
 int64_t* Hw_modmul_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint32_t degree);
+/* res = a - scalar                                       (hal.c:56) */
+int64_t* Hw_modsub_scalar(int64_t* res, int64_t* a, int64_t s, MODULUS* m, uint32_t degree);
 /* res[i] = val[order[i]]; `order` is what Auto_order returned */
 int64_t* Hw_rotate(int64_t* res, int64_t* val, int64_t* order, MODULUS* m, uint32_t degree);
 /* negacyclic NTT / inverse NTT of one limb of prime `mod_idx` (0..L+K-1),
@@ -410,6 +412,40 @@ POLY     Init_poly_by_opnd(POLY res, POLY opnd1, POLY opnd2, bool is_ext);
 POLY     Swk_c0(POLY res, size_t size, bool is_rot, int32_t rot_idx);
 POLY     Swk_c1(POLY res, size_t size, bool is_rot, int32_t rot_idx);
 POLY_ARR Precomp(POLY_ARR res, size_t size, POLY input);   /* rns_poly.c:459 */
+
+/* Single-limb polynomials of the LPOLY emit target
+ * (ant/include/lpoly/poly.h:18-143, ant/lpoly/src/poly.c).  `_data` is device
+ * memory, so the allocation helpers the reference keeps inline in its header
+ * are entry points here; operands are passed by value as there. */
+typedef struct {
+  uint32_t _ring_degree;
+  bool     _is_ntt;
+  int64_t* _data;
+} L_POLY;
+typedef L_POLY* LPOLY;
+typedef L_POLY* LPOLY_ARR;
+static inline uint32_t Get_lpoly_degree(LPOLY poly) { return poly->_ring_degree; }
+static inline int64_t* Get_lpoly_coeffs(LPOLY poly) { return poly->_data; }
+static inline bool     Is_lpoly_ntt(LPOLY poly) { return poly->_is_ntt; }
+static inline void     Set_lpoly_ntt(LPOLY poly, bool v) { poly->_is_ntt = v; }
+static inline bool     Is_lpoly_ntt_match(LPOLY a, LPOLY b) { return a->_is_ntt == b->_is_ntt; }
+void  Alloc_lpoly_data(LPOLY poly, uint32_t ring_degree);
+void  Init_lpoly_data(LPOLY poly, uint32_t ring_degree, int64_t* data);
+void  Free_lpoly_data(LPOLY poly);
+LPOLY Alloc_lpoly(uint32_t degree);
+void  Free_lpoly(LPOLY poly);
+void  Zero_lpoly(LPOLY poly);
+void  Copy_lpoly(LPOLY res, L_POLY poly);
+LPOLY Add_lpoly(LPOLY sum, L_POLY poly1, L_POLY poly2, MODULUS* mod);
+LPOLY Add_scalar(LPOLY res, L_POLY poly, int64_t scalar, MODULUS* mod);
+LPOLY Sub_lpoly(LPOLY res, L_POLY poly1, L_POLY poly2, MODULUS* mod);
+LPOLY Sub_scalar(LPOLY res, L_POLY poly, int64_t scalar, MODULUS* mod);
+LPOLY Mul_lpoly(LPOLY res, L_POLY poly1, L_POLY poly2, MODULUS* mod);
+LPOLY Mul_scalar(LPOLY res, L_POLY poly, int64_t scalar, MODULUS* mod);
+LPOLY Mac_lpoly(LPOLY res, L_POLY poly1, L_POLY poly2, MODULUS* mod);   /* res += poly1 * poly2 */
+LPOLY Mac_scalar(LPOLY res, L_POLY poly, int64_t scalar, MODULUS* mod); /* res += poly * scalar */
+void  Ntt(LPOLY res, L_POLY poly, size_t idx);   /* idx: Q primes first, then special primes */
+void  Intt(LPOLY res, L_POLY poly, size_t idx);
 
 /* Limb-sharded ciphertext operations for single-ciphertext latency on several
  * GPUs (no reference counterpart: the CPU runtime has no distributed mode).

@@ -101,3 +101,42 @@ def test_plaintexts_from_data_file(setup, cache_mb):
     finally:
         gpu.lib.Pt_mgr_fini()
         os.environ.pop("FHERT_PT_CACHE_MB", None)
+
+
+def test_pre_encoded_plaintext_file(setup, tmp_path):
+    """A DE_PLAINTEXT data file whose entries the reference's offline encoder
+    entry point (Encode_plain_buffer, ckks/src/plain.c:196-217) produced:
+    Pt_from_msg hands out those residues (uploaded once), Free_data leaves them."""
+    from ace_compiler_b200.msgfile import write_plaintext_file
+    ref, gpu, rt, _ = setup
+    rng = np.random.default_rng(8)
+    enc = ref.lib.Encode_plain_buffer
+    enc.argtypes, enc.restype = [C.c_void_p, C.c_size_t, C.c_uint32, C.c_uint32], C.c_void_p
+    cases = [(1024, 1, 4), (10, 2, 3), (512, 1, L)]
+    buffers, want = [], []
+    for k, (length, scale, level) in enumerate(cases):
+        vals = np.ascontiguousarray(rng.normal(0, 0.3, length).astype(np.float32))
+        buf = enc(vals.ctypes.data, length, scale, level)
+        size = C.c_uint32.from_address(buf + 12).value
+        raw = C.string_at(buf, 16 + size)
+        assert raw[:8] == b"ANTPLAIN"
+        buffers.append((f"p{k}", raw, scale, level))
+        head = C.sizeof(rt.PLAINTEXT)
+        want.append(np.frombuffer(raw[16 + head:16 + head + level * N * 8], dtype=np.int64)
+                    .reshape(level, N).copy())
+    path = str(tmp_path / "weights.pt")
+    write_plaintext_file(path, buffers)
+    try:
+        assert gpu.lib.Pt_mgr_init(path.encode())
+        for rounds in range(2):
+            for k, (length, scale, level) in enumerate(cases):
+                pt = rt.PLAINTEXT()
+                gpu.lib.Pt_from_msg(C.byref(pt), k, length, scale, level)
+                assert pt._poly._num_primes == level and pt._sf_degree == scale
+                assert np.array_equal(gpu.download(C.pointer(pt._poly)), want[k]), k
+                gpu.lib.Free_data(C.byref(pt._poly))
+        stats = [C.c_size_t() for _ in range(4)]
+        gpu.lib.Fhert_pt_cache_stats(*[C.byref(s) for s in stats])
+        assert [s.value for s in stats][0] == len(cases) and [s.value for s in stats][2] == len(cases)
+    finally:
+        gpu.lib.Pt_mgr_fini()

@@ -173,3 +173,80 @@ def test_mod_down_rescale(pair):
         assert np.array_equal(gpu.download(out), h_out.host(0)[: level - 1]), level
         gpu.free(ext)
         gpu.free(out)
+
+
+def test_lpoly_interface(pair):
+    """The single-limb interface of the LPOLY emit target (lpoly/poly.h:116-143)
+    against the reference functions of the same names: every operation on the
+    first and on the last prime (a special one), operands by value."""
+    ref, gpu, rt = pair
+    n, rng = gpu.N, np.random.default_rng(36)
+
+    class HostLpoly(C.Structure):
+        _fields_ = [("_ring_degree", C.c_uint32), ("_is_ntt", C.c_bool), ("_data", C.c_void_p)]
+
+    def host(a, is_ntt):
+        keep = np.ascontiguousarray(a, np.int64)
+        return HostLpoly(n, is_ntt, keep.ctypes.data), keep
+
+    def dev(a, is_ntt):
+        p = rt.L_POLY()
+        gpu.lib.Alloc_lpoly_data(C.byref(p), n)
+        tmp = gpu.new_poly(1, data=a.reshape(1, n))
+        gpu.lib.Copy_lpoly(C.byref(p), rt.L_POLY(n, is_ntt, tmp.contents._data))
+        gpu.free(tmp)
+        return p
+
+    def down(p):
+        tmp = gpu.new_poly(1)
+        view = rt.L_POLY(n, False, tmp.contents._data)
+        gpu.lib.Copy_lpoly(C.byref(view), p)
+        out = gpu.download(tmp)[0]
+        gpu.free(tmp)
+        return out
+
+    for idx in (0, gpu.L + gpu.K - 1):
+        q = gpu.primes[idx]
+        a = rng.integers(0, q, n, dtype=np.int64)
+        b = rng.integers(0, q, n, dtype=np.int64)
+        a[:2], b[:2] = (q - 1, 0), (q - 1, q - 1)
+        mod_ref, mod_gpu = ref.lib.Ref_modulus(idx), gpu.modulus(idx)
+        for name, scalar in (("Add_lpoly", None), ("Sub_lpoly", None), ("Mul_lpoly", None),
+                             ("Mac_lpoly", None), ("Add_scalar", 12345), ("Sub_scalar", 777),
+                             ("Mul_scalar", q - 2), ("Mac_scalar", 99)):
+            res0 = rng.integers(0, q, n, dtype=np.int64)
+            hr, keep_r = host(res0.copy(), True)
+            ha, _ka = host(a, True)
+            hb, _kb = host(b, True)
+            f = getattr(ref.lib, name)
+            f.restype = C.c_void_p
+            dr, da, db = dev(res0, True), dev(a, True), dev(b, True)
+            if scalar is None:
+                f.argtypes = [C.c_void_p, HostLpoly, HostLpoly, C.c_void_p]
+                f(C.byref(hr), ha, hb, mod_ref)
+                getattr(gpu.lib, name)(C.byref(dr), da, db, mod_gpu)
+            else:
+                f.argtypes = [C.c_void_p, HostLpoly, C.c_int64, C.c_void_p]
+                f(C.byref(hr), ha, scalar, mod_ref)
+                getattr(gpu.lib, name)(C.byref(dr), da, scalar, mod_gpu)
+            assert np.array_equal(down(dr), keep_r), (name, idx)
+            assert bool(dr._is_ntt) == bool(hr._is_ntt)
+            for p in (dr, da, db):
+                gpu.lib.Free_lpoly_data(C.byref(p))
+        # transforms: coefficient form -> NTT -> back
+        hc, keep_c = host(a.copy(), False)
+        hn, keep_n = host(np.zeros(n, np.int64), False)
+        for fn in (ref.lib.Ntt, ref.lib.Intt):
+            fn.argtypes, fn.restype = [C.c_void_p, HostLpoly, C.c_size_t], None
+        ref.lib.Ntt(C.byref(hn), hc, idx)
+        dc, dn = dev(a, False), dev(np.zeros(n, np.int64), False)
+        gpu.lib.Ntt(C.byref(dn), dc, idx)
+        assert dn._is_ntt and np.array_equal(down(dn), keep_n), idx
+        gpu.lib.Intt(C.byref(dc), dn, idx)
+        assert not dc._is_ntt and np.array_equal(down(dc), a), idx
+        for p in (dc, dn):
+            gpu.lib.Free_lpoly_data(C.byref(p))
+    heap = gpu.lib.Alloc_lpoly(n)
+    assert heap.contents._is_ntt and heap.contents._ring_degree == n
+    assert np.count_nonzero(down(heap.contents)) == 0
+    gpu.lib.Free_lpoly(heap)
