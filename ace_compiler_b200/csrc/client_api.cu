@@ -168,7 +168,8 @@ std::vector<int64_t> encode_value(Context* c, double value, uint32_t level, doub
 // ckks/src/encoder.c:234-325; slots = 0 means N/2, num_p = K also fills the
 // special limbs (the plaintexts of the bootstrapping linear transforms)
 void encode_vector(Context* c, PLAIN plain, std::vector<cplx>& values, uint32_t sf_degree,
-                   uint32_t level, uint32_t slots, uint32_t num_p) {
+                   uint32_t level, uint32_t slots, uint32_t num_p, const float* reals,
+                   size_t real_count) {
   ensure_fft_tables(c);
   const uint32_t n = c->N;
   if (slots == 0) slots = n / 2;
@@ -177,7 +178,8 @@ void encode_vector(Context* c, PLAIN plain, std::vector<cplx>& values, uint32_t 
   const uint32_t gap = n / (slots * 2);
   if (level == 0) level = c->L;
   FHERT_ASSERT(level <= (uint32_t)c->L, "level should not be larger than mul_depth + 1");
-  FHERT_ASSERT(values.size() <= slots, "slot size is too small");
+  const size_t count = reals != nullptr ? real_count : values.size();
+  FHERT_ASSERT(count <= slots, "slot size is too small");
   FHERT_ASSERT(sf_degree >= 1, "invalid scaling factor for encode");
   const double delta = std::pow(2.0, (double)c->sf_bits);
   init_plain(c, plain, level, std::pow(delta, (double)sf_degree), sf_degree, slots, num_p);
@@ -186,7 +188,7 @@ void encode_vector(Context* c, PLAIN plain, std::vector<cplx>& values, uint32_t 
   CUDA_CHECK(dev_alloc(&d_msg, n * sizeof(int64_t), c->stream));
   // inverse embedding, scaling and rounding run on the device with the host
   // routine's arithmetic (encode_gpu.cu)
-  encode_message_on_device(c, values.data(), values.size(), slots, d_msg);
+  encode_message_on_device(c, values.data(), count, slots, d_msg, reals);
   std::vector<u64> powp;
   if (sf_degree > 1) {
     // Delta^(d-1) modulo every prime (encoder.c:297-312)
@@ -273,9 +275,8 @@ void Encode_float(PLAIN plain, float* input, size_t len, uint32_t sc_degree, uin
     encode_scalar(c, plain, (double)*input, sc_degree, level);
     return;
   }
-  std::vector<cplx> v(len);
-  for (size_t i = 0; i < len; i++) v[i] = cplx((double)input[i], 0.0);
-  encode_vector(c, plain, v, sc_degree, level);
+  std::vector<cplx> none;  // the floats are widened to complex doubles on the device
+  encode_vector(c, plain, none, sc_degree, level, 0, 0, input, len);
 }
 
 void Encode_dcmplx(PLAIN plain, double* re_im, size_t len, uint32_t sc_degree, uint32_t level) {

@@ -50,20 +50,18 @@ __device__ __forceinline__ u64 mul_shoup(u64 a, u64 w, u64 wp, u64 q) {
   return r >= q ? r - q : r;
 }
 
-// Canonical a*b mod q for a, b < 2^61 (product below 2^122).  Single-word
-// Barrett: the quotient estimate is taken from the product shifted right by
-// bits-1, multiplied by bar = floor(2^(bits-1+64)/q); it undershoots the true
-// quotient by at most 2.
-__device__ __forceinline__ u64 mul_mod(u64 a, u64 b, const DevModulus& m) {
-  u64      lo = a * b;
-  u64      hi = __umul64hi(a, b);
-  uint32_t s  = m.bits - 1;
-  u64      x1 = (hi << (64 - s)) | (lo >> s);
-  u64      qh = __umul64hi(x1, m.bar);
-  u64      r  = lo - qh * m.q;
-  if (r >= 2 * m.q) r -= 2 * m.q;
-  if (r >= m.q) r -= m.q;
-  return r;
+// Exact 128-bit product of a, b < 2^61 from four 32x32 multiplies: with the high
+// halves below 2^29 the two middle products sum without overflow, so the only
+// carry is the one out of the low word.
+__device__ __forceinline__ void mul_wide_128(u64 a, u64 b, u64& hi, u64& lo) {
+  uint32_t a0 = (uint32_t)a, a1 = (uint32_t)(a >> 32), b0 = (uint32_t)b, b1 = (uint32_t)(b >> 32);
+  u64      t, mid, top;
+  asm("mul.wide.u32 %0, %1, %2;" : "=l"(t) : "r"(a0), "r"(b0));
+  asm("mul.wide.u32 %0, %1, %2;" : "=l"(mid) : "r"(a1), "r"(b0));
+  asm("mad.wide.u32 %0, %1, %2, %0;" : "+l"(mid) : "r"(a0), "r"(b1));
+  asm("mul.wide.u32 %0, %1, %2;" : "=l"(top) : "r"(a1), "r"(b1));
+  lo = t + (mid << 32);
+  hi = top + (mid >> 32) + (lo < t);
 }
 
 // floor(a*b / 2^64) or up to 2 less, from three 32x32 products: the exact
@@ -75,6 +73,23 @@ __device__ __forceinline__ u64 mulhi_under(u64 a, u64 b) {
   u64      t;
   asm("mul.wide.u32 %0, %1, %2;" : "=l"(t) : "r"(a1), "r"(b1));
   return t + m1 + m2;
+}
+
+// Canonical a*b mod q for a, b < 2^61 (product below 2^122).  Single-word
+// Barrett: the quotient estimate is taken from the product shifted right by
+// bits-1, multiplied by bar = floor(2^(bits-1+64)/q); with the three-product
+// high multiply it undershoots the true quotient by at most 4.
+__device__ __forceinline__ u64 mul_mod(u64 a, u64 b, const DevModulus& m) {
+  u64 hi, lo;
+  mul_wide_128(a, b, hi, lo);
+  uint32_t s  = m.bits - 1;
+  u64      x1 = (hi << (64 - s)) | (lo >> s);
+  u64      qh = mulhi_under(x1, m.bar);
+  u64      r  = lo - qh * m.q;
+  if (r >= 4 * m.q) r -= 4 * m.q;
+  if (r >= 2 * m.q) r -= 2 * m.q;
+  if (r >= m.q) r -= m.q;
+  return r;
 }
 
 // Canonical reduction of a 128-bit value (hi:lo) < 2^127 with the two-word
@@ -94,8 +109,8 @@ __device__ __forceinline__ u64 reduce_128(u64 hi, u64 lo, const DevModulus& m) {
 
 // acc(hi:lo) += a*b
 __device__ __forceinline__ void mac_128(u64& hi, u64& lo, u64 a, u64 b) {
-  u64 pl = a * b;
-  u64 ph = __umul64hi(a, b);
+  u64 ph, pl;
+  mul_wide_128(a, b, ph, pl);
   lo += pl;
   hi += ph + (lo < pl);
 }

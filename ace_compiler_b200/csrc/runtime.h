@@ -249,15 +249,17 @@ void dev_release_all(cudaStream_t stream);  // gives every kept block back to th
 // ---- encode_gpu.cu ----
 // inverse embedding, scaling and rounding of `count` complex slot values (host)
 // into the message polynomial d_msg (N int64 on the device)
+// (`reals`, when given, replaces `values`: count real single-precision inputs)
 void encode_message_on_device(Context* c, const std::complex<double>* values, size_t count,
-                              uint32_t slots, int64_t* d_msg);
+                              uint32_t slots, int64_t* d_msg, const float* reals = nullptr);
 void free_encode_tables(Context* c);
 
 // ---- client_api.cu ----
 // encode at sf_degree and level; slots = 0 means N/2, num_p = K also fills
 // the special limbs (stored right behind the level Q limbs)
 void encode_vector(Context* c, PLAIN plain, std::vector<std::complex<double>>& values,
-                   uint32_t sf_degree, uint32_t level, uint32_t slots = 0, uint32_t num_p = 0);
+                   uint32_t sf_degree, uint32_t level, uint32_t slots = 0, uint32_t num_p = 0,
+                   const float* reals = nullptr, size_t real_count = 0);
 // residues of one real value at the given scale on level Q limbs then num_p
 // special limbs
 std::vector<int64_t> encode_value(Context* c, double value, uint32_t level, double scale,
