@@ -35,14 +35,13 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
-    if world > 1:
-        import torch.distributed as dist
-        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     n, L = args.degree, args.levels
     saved = os.dup(1)
     os.dup2(2, 1)  # the library and NCCL print their greeting lines with C stdio
     if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist.barrier()
     gpu = rt.Runtime(n, L, 60, 56, 3, rot_idxs=(1,))
     lib = gpu.lib

@@ -204,8 +204,8 @@ def run_primitives(args):
     torch.cuda.set_device(local)
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         with c_stdout_to_stderr():  # NCCL prints its version line when the communicator is made
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
             dist.barrier()
 
     with c_stdout_to_stderr():
@@ -470,8 +470,8 @@ def run_resnet20(args):
     torch.cuda.set_device(local)
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         with c_stdout_to_stderr():  # NCCL prints its version line when the communicator is made
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
             dist.barrier()
 
     from ace_compiler_b200.msgfile import write_synthetic_msg_file
@@ -700,8 +700,8 @@ def run_bootstrap(args):
     torch.cuda.set_device(local)
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         with c_stdout_to_stderr():  # NCCL prints its version line when the communicator is made
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
             dist.barrier()
     os.environ["RTLIB_DISABLE_BOOTSTRAP_PRECOM"] = "0"
     t0 = time.perf_counter()
