@@ -265,6 +265,8 @@ SIGNATURES = {
     "Free_data": (None, [C.c_void_p]),
     "Fhert_pt_cache_stats": (None, [C.POINTER(C.c_size_t)] * 4),
     "Fhert_pt_cache_bypass": (None, [C.c_int]),
+    "Fhert_replay_mode": (None, [C.c_int]),
+    "Fhert_replay_state": (C.c_int, [C.c_char_p, C.c_size_t, C.POINTER(C.c_uint64)]),
     "Validate_impl": (None, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.c_uint32, C.c_int32]),
     "Validate_value_range": (None, [C.c_bool]),
     "Within_value_range": (C.c_bool, [CIPHER, C.POINTER(C.c_double), C.c_uint32]),

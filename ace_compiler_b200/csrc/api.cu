@@ -295,10 +295,10 @@ void Fhert_download(POLY poly, size_t first, size_t limbs, int64_t* host) {
   size_t n = poly->_ring_degree;
   CUDA_CHECK(counted_copy(host, poly->_data + first * n, limbs * n * sizeof(int64_t),
                              cudaMemcpyDeviceToHost, ctx()->stream));
-  CUDA_CHECK(cudaStreamSynchronize(ctx()->stream));
+  CUDA_CHECK(stream_sync(ctx()->stream));
 }
 
-void     Fhert_sync(void) { CUDA_CHECK(cudaStreamSynchronize(ctx()->stream)); }
+void     Fhert_sync(void) { CUDA_CHECK(stream_sync(ctx()->stream)); }
 void*    Fhert_stream(void) { return (void*)ctx()->stream; }
 uint64_t Fhert_kernel_launches(void) { return ctx_or_null() ? ctx()->launches : 0; }
 void     Fhert_transfer_bytes(uint64_t* h2d, uint64_t* d2h) {
@@ -954,7 +954,7 @@ void Fhert_import_switch_key(bool is_rot, int32_t rot_idx, uint32_t part, int wh
   POLY   p     = which == 0 ? &k->_parts[part]._p0 : &k->_parts[part]._p1;
   size_t bytes = (size_t)(c->L + c->K) * c->N * sizeof(int64_t);
   CUDA_CHECK(counted_copy(p->_data, host, bytes, cudaMemcpyHostToDevice, c->stream));
-  CUDA_CHECK(cudaStreamSynchronize(c->stream));
+  CUDA_CHECK(stream_sync(c->stream));
 }
 
 

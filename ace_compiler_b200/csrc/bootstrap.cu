@@ -378,7 +378,7 @@ Precom* setup(Context* c, uint32_t slots) {
 
   Stages dec = merged_stages(ksi, rot_group, budget[1], false, false, full);
   pre->s2c   = encode_stages(c, dec, pre->dec, scale_dec, level_dec, false);
-  CUDA_CHECK(cudaStreamSynchronize(c->stream));
+  CUDA_CHECK(stream_sync(c->stream));
   return pre;
 }
 
@@ -534,7 +534,7 @@ static POLYNOMIAL* monomial_ntt(Context* c, uint32_t reduced) {
   for (size_t i = 0; i < level; i++)
     CUDA_CHECK(counted_copy(mono._data + i * n + index, &one[i], sizeof(int64_t),
                                cudaMemcpyHostToDevice, c->stream));
-  CUDA_CHECK(cudaStreamSynchronize(c->stream));
+  CUDA_CHECK(stream_sync(c->stream));
   Conv_poly2ntt_inplace(&mono);
   return &table.emplace(reduced, mono).first->second;
 }

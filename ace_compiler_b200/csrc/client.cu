@@ -126,7 +126,7 @@ int64_t* upload_samples(Context* c, const std::vector<int64_t>& v) {
   CUDA_CHECK(counted_copy(d, v.data(), v.size() * sizeof(int64_t), cudaMemcpyHostToDevice,
                              c->stream));
   // the host vector may go out of scope before the copy is consumed
-  CUDA_CHECK(cudaStreamSynchronize(c->stream));
+  CUDA_CHECK(stream_sync(c->stream));
   return d;
 }
 
@@ -152,7 +152,7 @@ void sample_uniform_poly(Context* c, POLY a) {
     sample_uniform(host.data() + (a->_num_primes + k) * c->N, c->N, c->primes[c->L + k]);
   CUDA_CHECK(counted_copy(a->_data, host.data(), host.size() * sizeof(int64_t),
                              cudaMemcpyHostToDevice, c->stream));
-  CUDA_CHECK(cudaStreamSynchronize(c->stream));
+  CUDA_CHECK(stream_sync(c->stream));
 }
 
 // ckks/src/key_gen.c:127-200.  new_key may be in coefficient or NTT form and
@@ -240,7 +240,7 @@ void generate_keys(Context* c) {
   Alloc_poly_data(&c->sk_ntt, n, L, K);
   CUDA_CHECK(counted_copy(c->sk_s._data, host.data(), host.size() * sizeof(int64_t),
                              cudaMemcpyHostToDevice, c->stream));
-  CUDA_CHECK(cudaStreamSynchronize(c->stream));
+  CUDA_CHECK(stream_sync(c->stream));
   Copy_poly(&c->sk_ntt, &c->sk_s);
   c->sk_ntt._is_ntt = false;
   Conv_poly2ntt_inplace(&c->sk_ntt);
@@ -274,7 +274,7 @@ void generate_keys(Context* c) {
     if (c->keys.count(k)) continue;
     generate_rotation_key(c, k, false);
   }
-  CUDA_CHECK(cudaStreamSynchronize(c->stream));
+  CUDA_CHECK(stream_sync(c->stream));
 }
 
 // bootstrap.c:1199-1231: keys for the rotations of the linear transforms, in
@@ -288,7 +288,7 @@ void generate_bootstrap_keys(Context* c, const std::vector<int32_t>& rotations) 
   }
   uint32_t conj = 2 * c->N - 1;
   if (!c->keys.count(conj)) generate_rotation_key(c, conj, true);
-  CUDA_CHECK(cudaStreamSynchronize(c->stream));
+  CUDA_CHECK(stream_sync(c->stream));
 }
 
 void free_keys(Context* c) {

@@ -203,7 +203,8 @@ void encode_vector(Context* c, PLAIN plain, std::vector<cplx>& values, uint32_t 
                                cudaMemcpyHostToDevice, c->stream));
   }
   launch_encode_split(plain->_poly._data, d_msg, d_pow, q_batch(level, num_p, c->L));
-  if (d_pow) CUDA_CHECK(cudaStreamSynchronize(c->stream));  // powp lives on the host stack
+  // powp lives on the host stack (a captured copy reads its own snapshot instead)
+  if (d_pow && !image_capturing()) CUDA_CHECK(stream_sync(c->stream));
   CUDA_CHECK(dev_free(d_msg, c->stream));
   if (d_pow) CUDA_CHECK(dev_free(d_pow, c->stream));
   plain->_poly._is_ntt = false;
@@ -313,7 +314,7 @@ void error_poly(Context* c, POLY e, size_t level) {
                              c->stream));
   Alloc_poly_data(e, c->N, level, 0);
   launch_small_to_rns(e->_data, d, q_batch(level));
-  CUDA_CHECK(cudaStreamSynchronize(c->stream));
+  CUDA_CHECK(stream_sync(c->stream));
   CUDA_CHECK(dev_free(d, c->stream));
   e->_is_ntt = false;
 }

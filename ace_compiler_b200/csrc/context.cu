@@ -306,6 +306,7 @@ template <typename T>
 static T* upload(const std::vector<T>& v) {
   T* d = nullptr;
   if (v.empty()) return d;
+  if (image_capturing()) image_capture_break("a table built on first use");
   CUDA_CHECK(cudaMalloc(&d, v.size() * sizeof(T)));
   CUDA_CHECK(cudaMemcpy(d, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice));
   // a copy from pageable memory may still be in flight when cudaMemcpy returns,
@@ -581,6 +582,7 @@ Context* create_context(const CKKS_PARAMS* p) {
 void destroy_context() {
   Context* c = g_ctx;
   if (!c) return;
+  image_replay_release();  // its blocks join the common lists, released below
   hw_release(c);
   free_encode_tables(c);
   free_bootstrap(c);
@@ -656,6 +658,8 @@ void prof_after(KernelId, int limbs) {
   g_prof.used++;
 }
 
+bool prof_running() { return g_prof.on; }
+
 void prof_begin() {
   g_prof.on   = true;
   g_prof.used = 0;
@@ -665,7 +669,7 @@ void prof_begin() {
 
 // writes "name launches limbs total_ms" lines into buf; returns bytes written
 size_t prof_end(char* buf, size_t cap) {
-  CUDA_CHECK(cudaStreamSynchronize(ctx()->stream));
+  CUDA_CHECK(stream_sync(ctx()->stream));
   g_prof.on = false;
   double ms[KID_COUNT]  = {0};
   long   cnt[KID_COUNT] = {0};
@@ -693,19 +697,29 @@ namespace {
 struct DevPool {
   std::unordered_map<size_t, std::vector<void*>> free_by_size;
   std::unordered_map<void*, size_t>              size_of;
-  int                                            enabled = -1;
   size_t                                         held = 0;  // bytes waiting in the lists
-  size_t                                         cap  = (size_t)32 << 30;
 };
-DevPool g_pool;
+DevPool g_pool;     // everybody's blocks
+DevPool g_private;  // blocks of a captured program run
+bool    g_private_mode = false;
+int     g_pool_enabled = -1;
+size_t  g_pool_cap     = (size_t)32 << 30;
 bool pool_enabled() {
-  if (g_pool.enabled < 0) {
+  if (g_pool_enabled < 0) {
     const char* e  = std::getenv("FHERT_POOL");
-    g_pool.enabled = !(e != nullptr && e[0] == '0');
+    g_pool_enabled = !(e != nullptr && e[0] == '0');
     if (const char* mb = std::getenv("FHERT_POOL_MB"))
-      g_pool.cap = (size_t)std::strtoull(mb, nullptr, 10) << 20;
+      g_pool_cap = (size_t)std::strtoull(mb, nullptr, 10) << 20;
   }
-  return g_pool.enabled != 0;
+  return g_pool_enabled != 0;
+}
+bool take_from(DevPool& pool, size_t bytes, void** ptr) {
+  auto it = pool.free_by_size.find(bytes);
+  if (it == pool.free_by_size.end() || it->second.empty()) return false;
+  *ptr = it->second.back();
+  it->second.pop_back();
+  pool.held -= bytes;
+  return true;
 }
 }  // namespace
 
@@ -713,13 +727,13 @@ cudaError_t dev_alloc(void** ptr, size_t bytes, cudaStream_t stream) {
   if (!pool_enabled()) return cudaMallocAsync(ptr, bytes, stream);
   if (bytes == 0) bytes = 256;
   bytes = (bytes + 255) & ~(size_t)255;
-  auto it = g_pool.free_by_size.find(bytes);
-  if (it != g_pool.free_by_size.end() && !it->second.empty()) {
-    *ptr = it->second.back();
-    it->second.pop_back();
-    g_pool.held -= bytes;
-    return cudaSuccess;
+  if (g_private_mode) {
+    if (take_from(g_private, bytes, ptr)) return cudaSuccess;
+    cudaError_t err = cudaMalloc(ptr, bytes);
+    if (err == cudaSuccess) g_private.size_of[*ptr] = bytes;
+    return err;
   }
+  if (take_from(g_pool, bytes, ptr)) return cudaSuccess;
   cudaError_t err = cudaMallocAsync(ptr, bytes, stream);
   if (err == cudaErrorMemoryAllocation) {  // make room with what the lists hold
     cudaGetLastError();
@@ -733,11 +747,26 @@ cudaError_t dev_alloc(void** ptr, size_t bytes, cudaStream_t stream) {
 
 cudaError_t dev_free(void* ptr, cudaStream_t stream) {
   if (ptr == nullptr) return cudaSuccess;
+  auto mine = g_private.size_of.find(ptr);
+  if (mine != g_private.size_of.end()) {  // never trimmed: a replay may still use it
+    g_private.free_by_size[mine->second].push_back(ptr);
+    g_private.held += mine->second;
+    return cudaSuccess;
+  }
   auto it = g_pool.size_of.find(ptr);
   if (it == g_pool.size_of.end()) return cudaFreeAsync(ptr, stream);  // not from the lists
+  if (g_private_mode && image_capturing()) {
+    // the captured kernels used this block: from now on only a replay may
+    g_private.size_of[ptr] = it->second;
+    g_private.free_by_size[it->second].push_back(ptr);
+    g_private.held += it->second;
+    g_pool.size_of.erase(it);
+    return cudaSuccess;
+  }
   g_pool.free_by_size[it->second].push_back(ptr);
   g_pool.held += it->second;
-  if (g_pool.held > g_pool.cap) dev_release_all(stream);  // sizes no longer in use pile up
+  // sizes no longer in use pile up; not while a capture runs (a free would become a node)
+  if (g_pool.held > g_pool_cap && !image_capturing()) dev_release_all(stream);
   return cudaSuccess;
 }
 
@@ -749,6 +778,34 @@ void dev_release_all(cudaStream_t stream) {
     }
   g_pool.free_by_size.clear();
   g_pool.held = 0;
+}
+
+void dev_private_mode(bool on) { g_private_mode = on && pool_enabled(); }
+
+bool dev_take_private(void* ptr) {
+  auto mine = g_private.size_of.find(ptr);
+  if (mine == g_private.size_of.end()) return false;
+  auto& list = g_private.free_by_size[mine->second];
+  for (size_t i = list.size(); i-- > 0;)
+    if (list[i] == ptr) {
+      list.erase(list.begin() + (long)i);
+      g_private.held -= mine->second;
+      return true;
+    }
+  return false;
+}
+
+void dev_private_to_common(cudaStream_t stream) {
+  // cudaFreeAsync accepts blocks that came from cudaMalloc, so the common
+  // lists may hold them and give them back to the driver like their own
+  for (auto& kv : g_private.size_of) g_pool.size_of[kv.first] = kv.second;
+  for (auto& kv : g_private.free_by_size) {
+    auto& list = g_pool.free_by_size[kv.first];
+    list.insert(list.end(), kv.second.begin(), kv.second.end());
+  }
+  g_pool.held += g_private.held;
+  g_private = DevPool();
+  if (g_pool.held > g_pool_cap) dev_release_all(stream);
 }
 
 int64_t* scratch(size_t words) {

@@ -113,6 +113,7 @@ EncodeTables* tables_of(Context* c) {
   rot[0] = 1;
   for (size_t i = 1; i < slots; i++) rot[i] = (uint32_t)((5ull * rot[i - 1]) % m);
   EncodeTables* t = new EncodeTables();
+  if (image_capturing()) image_capture_break("a table built on first use");
   CUDA_CHECK(cudaMalloc(&t->roots, m * sizeof(double2)));
   CUDA_CHECK(cudaMalloc(&t->rot_group, slots * sizeof(uint32_t)));
   CUDA_CHECK(cudaMemcpy(t->roots, roots.data(), m * sizeof(double2), cudaMemcpyHostToDevice));

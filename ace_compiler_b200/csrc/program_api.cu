@@ -108,6 +108,81 @@ IoTable g_io;
 
 CIPHERTEXT* new_ciph() { return (CIPHERTEXT*)std::calloc(1, sizeof(CIPHERTEXT)); }
 
+// ---- replay of a program run -------------------------------------------------
+// A program run is a fixed sequence of launches: the program cannot branch on
+// encrypted data, and levels, scales and slot counts are the same for every
+// input.  With the replay mode on, the second Run_main_graph captures its
+// launches into one CUDA graph (while the host code of the program runs as
+// usual), and every later call copies the waiting inputs into the captured
+// input blocks, launches the graph and hands out the captured output blocks:
+// the host issues one launch per run instead of tens of thousands.
+struct PinnedCiph {
+  std::string name;
+  size_t      idx;
+  CIPHERTEXT  meta;  // host fields and device addresses at capture time
+};
+struct ImageReplay {
+  int                     mode        = -1;  // -1: FHERT_REPLAY not read yet, 0 off, 1 on
+  int                     direct_runs = 0;   // runs launched directly since the mode went on
+  bool                    capturing   = false;
+  cudaGraphExec_t         exec        = nullptr;
+  uint64_t                launches    = 0;  // launches of this library one replay stands for
+  uint64_t                replays     = 0;
+  std::vector<PinnedCiph> inputs, outputs;
+  std::string             why_off;
+  // pinned snapshots of the host data the captured run copies to the device
+  std::vector<char*>      stage_chunks;
+  size_t                  stage_used = 0, stage_total = 0;  // bytes used in the last chunk / overall
+};
+constexpr size_t kStageChunk = (size_t)32 << 20;
+ImageReplay g_replay;
+
+bool replay_on() {
+  if (g_replay.mode < 0) {
+    const char* e = std::getenv("FHERT_REPLAY");
+    g_replay.mode = e != nullptr && e[0] != '\0' && e[0] != '0';
+  }
+  return g_replay.mode == 1;
+}
+
+void replay_drop(const char* why) {
+  Context* c = ctx_noflush();
+  if (g_replay.exec != nullptr) {
+    CUDA_CHECK(cudaGraphExecDestroy(g_replay.exec));  // a launch in flight still completes
+    g_replay.exec = nullptr;
+  }
+  g_replay.inputs.clear();
+  g_replay.outputs.clear();
+  if (!g_replay.stage_chunks.empty()) {
+    CUDA_CHECK(cudaStreamSynchronize(c->stream));  // a launch in flight may still read them
+    for (char* p : g_replay.stage_chunks) CUDA_CHECK(cudaFreeHost(p));
+    g_replay.stage_chunks.clear();
+    g_replay.stage_used = g_replay.stage_total = 0;
+  }
+  g_replay.mode        = 0;
+  g_replay.direct_runs = 0;
+  if (why != nullptr) g_replay.why_off = why;
+  dev_private_mode(false);
+  dev_private_to_common(c->stream);
+}
+
+void launch_captured(Context* c, cudaGraph_t graph, bool keep) {
+  cudaGraphExec_t exec = nullptr;
+  CUDA_CHECK(cudaGraphInstantiate(&exec, graph, 0));
+  CUDA_CHECK(cudaGraphDestroy(graph));
+  CUDA_CHECK(cudaGraphLaunch(exec, c->stream));
+  if (keep)
+    g_replay.exec = exec;
+  else
+    CUDA_CHECK(cudaGraphExecDestroy(exec));
+}
+
+bool same_shape(const POLYNOMIAL& a, const POLYNOMIAL& b) {
+  return a._ring_degree == b._ring_degree && a._num_alloc_primes == b._num_alloc_primes &&
+         a._num_primes == b._num_primes && a._num_primes_p == b._num_primes_p &&
+         a._is_ntt == b._is_ntt;
+}
+
 double g_tm_stamp = 0;
 
 double wall_seconds() {
@@ -117,6 +192,51 @@ double wall_seconds() {
 }
 
 }  // namespace
+
+namespace fhert {
+bool image_capturing() { return g_replay.capturing; }
+
+const void* image_capture_stage(const void* src, size_t bytes) {
+  static size_t budget = [] {
+    const char* e = std::getenv("FHERT_REPLAY_STAGE_MB");
+    return (e != nullptr ? (size_t)std::strtoull(e, nullptr, 10) : (size_t)4096) << 20;
+  }();
+  const size_t need = (bytes + 255) & ~(size_t)255;
+  if (g_replay.stage_total + need > budget) return nullptr;
+  if (g_replay.stage_chunks.empty() || g_replay.stage_used + need > std::max(kStageChunk, need)) {
+    char* chunk = nullptr;
+    if (cudaMallocHost(&chunk, std::max(kStageChunk, need)) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    g_replay.stage_chunks.push_back(chunk);
+    g_replay.stage_used = 0;
+  }
+  char* at = g_replay.stage_chunks.back() + g_replay.stage_used;
+  std::memcpy(at, src, bytes);
+  g_replay.stage_used += need;
+  g_replay.stage_total += need;
+  return at;
+}
+
+void image_capture_break(const char* why) {
+  if (!g_replay.capturing) return;
+  g_replay.capturing = false;  // first: the calls below pass the same guards
+  Context*    c     = ctx_noflush();
+  cudaGraph_t graph = nullptr;
+  CUDA_CHECK(cudaStreamEndCapture(c->stream, &graph));
+  FHERT_ASSERT(graph != nullptr, "Run_main_graph: the capture of the program run was lost");
+  launch_captured(c, graph, false);
+  dev_private_mode(false);
+  g_replay.mode    = 0;
+  g_replay.why_off = std::string("the run cannot be captured: ") + why;
+}
+
+void image_replay_release() {
+  if (g_replay.mode == 1 || g_replay.exec != nullptr) replay_drop("the context was released");
+  g_replay = ImageReplay();
+}
+}  // namespace fhert
 
 extern "C" {
 
@@ -379,7 +499,8 @@ static bool tm_enabled() {
     const char* e = std::getenv("FHERT_RT_STAT");
     on            = !(e != nullptr && e[0] == '0');
   }
-  return on != 0;
+  // a timer line needs the device drained, which a captured run cannot do
+  return on != 0 && !replay_on();
 }
 
 void Tm_start(const char*) {
@@ -463,9 +584,144 @@ void Set_output_data(const char* name, size_t idx, CIPHER data) {
   slot[idx] = out;
 }
 
+// Launches the captured run on the inputs now waiting in the input table.
+static bool replay_run() {
+  Context* c = ctx();
+  for (const PinnedCiph& in : g_replay.inputs) {
+    auto it = g_io.inputs.find(in.name);
+    if (it == g_io.inputs.end() || in.idx >= it->second.size() || !it->second[in.idx]) return false;
+    const CIPHERTEXT* x = it->second[in.idx];
+    if (!same_shape(x->_c0_poly, in.meta._c0_poly) || !same_shape(x->_c1_poly, in.meta._c1_poly) ||
+        x->_slots != in.meta._slots || x->_sf_degree != in.meta._sf_degree ||
+        x->_scaling_factor != in.meta._scaling_factor)
+      return false;
+  }
+  for (const PinnedCiph& in : g_replay.inputs) {
+    CIPHERTEXT*& x = g_io.inputs[in.name][in.idx];
+    const POLYNOMIAL* src[2] = {&x->_c0_poly, &x->_c1_poly};
+    const POLYNOMIAL* dst[2] = {&in.meta._c0_poly, &in.meta._c1_poly};
+    for (int k = 0; k < 2; k++)
+      CUDA_CHECK(counted_copy(dst[k]->_data, src[k]->_data,
+                              src[k]->_num_alloc_primes * (size_t)c->N * sizeof(int64_t),
+                              cudaMemcpyDeviceToDevice, c->stream));
+    Free_ciph_poly(x, 1);  // the program would have taken and freed it
+    std::free(x);
+    x = nullptr;
+  }
+  CUDA_CHECK(cudaGraphLaunch(g_replay.exec, c->stream));
+  c->launches += g_replay.launches;
+  g_replay.replays++;
+  for (const PinnedCiph& out : g_replay.outputs) {
+    auto& slot = g_io.outputs[out.name];
+    if (slot.size() <= out.idx) slot.resize(out.idx + 1, nullptr);
+    if (slot[out.idx] != nullptr) {  // the result of the run before was never fetched
+      Free_ciph_poly(slot[out.idx], 1);
+      std::free(slot[out.idx]);
+    }
+    CIPHERTEXT* o = new_ciph();
+    *o            = out.meta;
+    dev_take_private(o->_c0_poly._data);
+    dev_take_private(o->_c1_poly._data);
+    slot[out.idx] = o;
+  }
+  return true;
+}
+
+// Runs the program once with its launches captured, then launches the capture.
+static void capture_run() {
+  Context* c = ctx();
+  c->raised.valid = false;
+  if (c->scratch) {  // so that the scratch the captured kernels use is a private block
+    CUDA_CHECK(dev_free(c->scratch, c->stream));
+    c->scratch       = nullptr;
+    c->scratch_words = 0;
+  }
+  dev_private_mode(true);
+  g_replay.inputs.clear();
+  g_replay.outputs.clear();
+  for (auto& kv : g_io.inputs)
+    for (size_t i = 0; i < kv.second.size(); i++) {
+      if (kv.second[i] == nullptr) continue;
+      CIPHERTEXT* pinned = new_ciph();  // a private copy: replays write the next input here
+      Copy_ciph(pinned, kv.second[i]);
+      Free_ciph_poly(kv.second[i], 1);
+      std::free(kv.second[i]);
+      kv.second[i] = pinned;
+      g_replay.inputs.push_back(PinnedCiph{kv.first, i, *pinned});
+    }
+  for (auto& kv : g_io.outputs)
+    for (CIPHERTEXT*& o : kv.second)
+      if (o != nullptr) {  // left over from a run nobody fetched
+        Free_ciph_poly(o, 1);
+        std::free(o);
+        o = nullptr;
+      }
+  c = ctx();
+  const uint64_t launches0 = c->launches;
+  CUDA_CHECK(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeRelaxed));
+  g_replay.capturing = true;
+  bool ok = Main_graph();
+  c       = ctx();  // work still deferred belongs to this run
+  c->raised.valid = false;
+  if (g_replay.capturing) {
+    g_replay.capturing = false;
+    cudaGraph_t graph  = nullptr;
+    CUDA_CHECK(cudaStreamEndCapture(c->stream, &graph));
+    FHERT_ASSERT(graph != nullptr, "Run_main_graph: the capture of the program run was lost");
+    launch_captured(c, graph, true);
+    g_replay.launches = c->launches - launches0;
+    for (auto& kv : g_io.outputs)
+      for (size_t i = 0; i < kv.second.size(); i++)
+        if (kv.second[i] != nullptr) g_replay.outputs.push_back(PinnedCiph{kv.first, i, *kv.second[i]});
+    dev_private_mode(false);
+  } else {
+    replay_drop(nullptr);  // the capture was ended on the way; the reason is already noted
+  }
+  FHERT_ASSERT(ok, "run Main_graph failed");
+}
+
 void Run_main_graph(void) {
+  if (replay_on() && !prof_running()) {
+    if (g_replay.exec != nullptr) {
+      if (replay_run()) return;
+      replay_drop("the waiting inputs do not match the captured ones");
+    } else if (g_replay.direct_runs >= 1) {
+      // the first run filled the caches and built the tables made on first use
+      capture_run();
+      return;
+    }
+  }
+  if (g_replay.mode == 1) g_replay.direct_runs++;
   bool ok = Main_graph();
   FHERT_ASSERT(ok, "run Main_graph failed");
+}
+
+// No counterpart in the CPU runtime.  on != 0: the next but one Run_main_graph
+// is captured and later ones replay it (see the comment on ImageReplay);
+// on == 0: the capture is dropped and runs are launched directly again.
+// FHERT_REPLAY=1 in the environment switches the mode on at the first run.
+void Fhert_replay_mode(int on) {
+  ctx();
+  if (on) {
+    if (g_replay.mode != 1) {
+      g_replay.mode        = 1;
+      g_replay.direct_runs = 0;
+      g_replay.why_off.clear();
+    }
+  } else if (g_replay.mode == 1 || g_replay.exec != nullptr) {
+    replay_drop("switched off");
+  } else {
+    g_replay.mode = 0;
+  }
+}
+
+// 0: off (why, when given, receives the reason the mode went off by itself),
+// 1: on, nothing captured yet, 2: a captured run is being replayed.
+int Fhert_replay_state(char* why, size_t cap, uint64_t* replays) {
+  if (why != nullptr && cap > 0) std::snprintf(why, cap, "%s", g_replay.why_off.c_str());
+  if (replays != nullptr) *replays = g_replay.replays;
+  if (!replay_on()) return 0;
+  return g_replay.exec != nullptr ? 2 : 1;
 }
 
 double* Handle_output(const char* name) {

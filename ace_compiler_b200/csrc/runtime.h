@@ -196,6 +196,7 @@ inline cudaError_t counted_copy(void* dst, const void* src, size_t bytes, cudaMe
 Context* ctx_or_null();
 int64_t* scratch(size_t words);  // stream-ordered scratch, grows on demand
 void     prof_begin();
+bool     prof_running();
 size_t   prof_end(char* buf, size_t cap);
 
 // ---- host number theory (context.cu) ----
@@ -245,6 +246,35 @@ inline cudaError_t dev_alloc(T** ptr, size_t bytes, cudaStream_t stream) {
   return dev_alloc(reinterpret_cast<void**>(ptr), bytes, stream);
 }
 void dev_release_all(cudaStream_t stream);  // gives every kept block back to the driver
+// A second set of lists serves the requests made while a whole program run is
+// captured for replay (program_api.cu): blocks the captured kernels use must
+// never be handed to anybody else between two replays.  While the private mode
+// is on, a size the private lists do not hold comes from cudaMalloc (legal
+// inside a relaxed capture, unlike a stream-ordered allocation, which would
+// become a node of the graph); a block goes back to the lists it came from
+// whatever the mode.
+void dev_private_mode(bool on);
+bool dev_take_private(void* ptr);            // takes one given block out of the private lists
+void dev_private_to_common(cudaStream_t s);  // ends the separation: every private block joins the common lists
+
+// ---- program_api.cu: a captured program run ----
+// True while Run_main_graph is capturing the launches of a program run.
+bool image_capturing();
+// Ends a running capture because `why` cannot be captured (a copy from or to
+// host memory, a synchronisation): what was captured so far is launched at
+// once, the rest of the run is launched directly and the replay mode goes off.
+void image_capture_break(const char* why);
+// A copy of host data into pinned memory that lives as long as the captured
+// run: a captured host-to-device copy reads the snapshot at every replay (the
+// host data of a program run, constants and weights, are the same in every
+// run).  nullptr when the budget for such snapshots is used up.
+const void* image_capture_stage(const void* src, size_t bytes);
+void image_replay_release();  // drops a captured run (context teardown)
+// cudaStreamSynchronize that first ends a running capture
+inline cudaError_t stream_sync(cudaStream_t stream) {
+  if (image_capturing()) image_capture_break("a synchronisation");
+  return cudaStreamSynchronize(stream);
+}
 
 // ---- encode_gpu.cu ----
 // inverse embedding, scaling and rounding of `count` complex slot values (host)
@@ -442,6 +472,15 @@ namespace fhert {
 inline cudaError_t counted_copy(void* dst, const void* src, size_t bytes, cudaMemcpyKind kind,
                                 cudaStream_t stream) {
   Context* c = ctx_or_null();
+  if (kind != cudaMemcpyDeviceToDevice && image_capturing()) {
+    const void* kept = kind == cudaMemcpyHostToDevice ? image_capture_stage(src, bytes) : nullptr;
+    if (kept != nullptr)
+      src = kept;
+    else
+      image_capture_break(kind == cudaMemcpyHostToDevice
+                              ? "more host data to copy than the snapshot budget (FHERT_REPLAY_STAGE_MB)"
+                              : "a copy to host memory");
+  }
   if (c != nullptr) {
     if (kind == cudaMemcpyHostToDevice) c->h2d_bytes += bytes;
     else if (kind == cudaMemcpyDeviceToHost) c->d2h_bytes += bytes;

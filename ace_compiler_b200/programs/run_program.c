@@ -16,7 +16,9 @@
  *   {"image": i, "encrypt_s": .., "infer_s": .., "decrypt_s": .., "logits": [..]}
  * and a final line {"setup_s": .., "images": k, "mean_infer_s": ..}.
  * FHERT_DATA_FILE=<path> replaces the weight file path compiled into the
- * program. */
+ * program.  FHERT_REPLAY=1 captures the second image's Main_graph as one CUDA
+ * graph and replays it for the following images (B200 runtime only); the final
+ * line says how many runs the graph served. */
 #include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -130,8 +132,17 @@ int main(int argc, char** argv) {
     free(out);
     total += c - b;
   }
-  printf("{\"setup_s\": %.3f, \"images\": %d, \"mean_infer_s\": %.6f}\n", setup, images,
-         total / (images > 0 ? images : 1));
+  unsigned long long replayed = 0;
+  int                replay_state = 0;
+  char               why[200]     = "";
+#ifndef REFERENCE_RUNTIME
+  uint64_t runs = 0;
+  replay_state  = Fhert_replay_state(why, sizeof(why), &runs);
+  replayed      = runs;
+#endif
+  printf("{\"setup_s\": %.3f, \"images\": %d, \"mean_infer_s\": %.6f, \"replay_state\": %d, "
+         "\"replayed_runs\": %llu, \"replay_off_because\": \"%s\"}\n",
+         setup, images, total / (images > 0 ? images : 1), replay_state, replayed, why);
   Finalize_context();
   return 0;
 }

@@ -543,6 +543,31 @@ void       Set_output_data(const char* name, size_t idx, CIPHER data); /* copies
 void       Run_main_graph(void);
 double*    Handle_output(const char* name);              /* malloc'ed, caller frees */
 
+/* Replay of a program run.  No counterpart in the CPU runtime.  A program
+ * cannot branch on encrypted data, so every run of Main_graph issues the same
+ * launches on the same device blocks.  With the mode on (this call, or
+ * FHERT_REPLAY=1 in the environment), the first Run_main_graph runs as usual
+ * (it fills the plaintext cache and builds the tables made on first use), the
+ * second one captures its launches into one CUDA graph while the program's
+ * host code runs, and every later one copies the inputs waiting from
+ * Prepare_input into the captured input blocks, launches the graph and
+ * registers the captured output blocks for Handle_output: one launch per run
+ * from the host instead of tens of thousands.  The blocks the captured
+ * launches use are kept apart from all other allocations until the mode goes
+ * off.  Host data the run copies to the device (constants it encodes, weights
+ * when the plaintext cache is off) are snapshotted in pinned memory at capture
+ * time, up to FHERT_REPLAY_STAGE_MB (4096) MiB, and replays read the snapshots.
+ * The mode goes off by itself, and the run is launched directly, when
+ * something in the run cannot be captured (a copy to host memory, a
+ * synchronisation, more host data than the snapshot budget);
+ * Fhert_replay_state reports it.  The per-operator
+ * timer lines (Tm_taken) are off while the mode is on.  Between two replayed
+ * runs fetch the result (Handle_output) before the next run overwrites it. */
+void Fhert_replay_mode(int on);
+/* 0 off (why receives the reason when the mode went off by itself), 1 on and
+ * nothing captured yet, 2 replaying; replays = runs served by the graph */
+int  Fhert_replay_state(char* why, size_t cap, uint64_t* replays);
+
 /* Weight data file named by Get_rt_data_info (message files of floats,
  * fhe-cmplr/include/fhe/core/rt_data_def.h:91-112; opened by Prepare_context)
  * and the plaintexts encoded from it (ant/porting/pt_mgr.c:179-214).

@@ -11,6 +11,9 @@ bootstraps), the workload the benchmark times.
   program, pinned randomness, input and weight file
   (tests/golden/make_resnet20_reference.sh wrote it); the GPU run must
   reproduce them bit for bit.
+* replayed against direct: with FHERT_REPLAY=1 the second image's Main_graph is
+  captured as one CUDA graph and the following images are served by launching
+  it; every image must give the logits of the directly launched run.
 """
 import json
 import os
@@ -69,3 +72,22 @@ def test_logits_equal_the_reference_runtime(recorded):
         golden = json.load(f)
     assert golden["args"] == ARGS and golden["weights"] == WEIGHTS
     assert recorded[0] == golden["logits"]
+
+
+def run_images(weights, images, **env):
+    e = dict(os.environ, FHERT_DATA_FILE=weights, FHERT_RT_STAT="0")
+    e.update(env)
+    args = ["--pin", "9", "--seed", "5", "--images", str(images), "--values", "10"]
+    out = subprocess.run([EXE] + args, capture_output=True, text=True, timeout=1500, env=e)
+    assert out.returncode == 0, (out.stdout + out.stderr)[-2000:]
+    lines = [json.loads(ln) for ln in out.stdout.splitlines() if ln.startswith("{")]
+    return [ln["logits"] for ln in lines if "image" in ln], lines[-1]
+
+
+def test_replayed_runs_equal_direct_runs(recorded, weights):
+    direct, _ = run_images(weights, 4, FHERT_PT_CACHE_MB="20000")
+    replayed, summary = run_images(weights, 4, FHERT_PT_CACHE_MB="20000", FHERT_REPLAY="1")
+    assert summary["replay_state"] == 2, summary
+    assert summary["replayed_runs"] == 2      # image 0 direct, image 1 captured, 2 and 3 replayed
+    assert direct[0] == recorded[0]
+    assert replayed == direct
