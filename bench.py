@@ -851,9 +851,10 @@ def run_bootstrap(args):
 # ---------------------------------------------------------------------------
 
 # DRAM bytes (read + write) per limb of a forward transform pair, from a profiler
-# capture of the two kernels on 48 limbs (25.2 MB strided + 33.6 MB contiguous per
-# launch pair); this run does not measure DRAM traffic itself
-NTT_DRAM_BYTES_PER_LIMB_CAPTURED = (25.2e6 + 33.6e6) / 48
+# capture of the two kernels on 48 limbs with cold caches (25.4 MB strided + 77.1 MB
+# contiguous per launch pair, twiddles included); this run does not measure DRAM
+# traffic itself
+NTT_DRAM_BYTES_PER_LIMB_CAPTURED = (25.4e6 + 77.1e6) / 48
 
 # What one image of the compiled ResNet-20 program executes, by operation class
 # (static analysis of the loop nests of the generated file): the CPU figures are
