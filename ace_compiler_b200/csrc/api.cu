@@ -540,7 +540,13 @@ POLY Rescale(POLY res, POLY poly) {
   size_t level = poly->_num_primes;
   FHERT_ASSERT(level >= 2, "Level of rescale opnd is too small");
   FHERT_ASSERT(res->_num_primes == level && res->_data, "Rescale: primes not match");
-  FHERT_ASSERT(poly->_is_ntt, "Rescale: coefficient-form input is not supported");
+  if (!poly->_is_ntt) {  // rns_poly.c:381-399: stays in coefficient form
+    ctx();
+    launch_rescale_coeff(ptr2(res->_data), ptr2(poly->_data), 1, (int)level);
+    res->_is_ntt     = false;
+    res->_num_primes = level - 1;
+    return res;
+  }
   pair_submit(2, res->_data, poly->_data, level, 0, true);
   res->_is_ntt     = true;
   res->_num_primes = level - 1;  // Modswitch(res, res)
@@ -1105,12 +1111,17 @@ CIPHER Rescale_ciph(CIPHER res, CIPHER ciph) {
   Context* c     = ctx();
   size_t   level = Level(ciph);
   FHERT_ASSERT(level > 1, "rescale: multiply level is not big enough");
-  FHERT_ASSERT(ciph->_c0_poly._is_ntt, "Rescale_ciph: coefficient form is not supported");
+  FHERT_ASSERT(ciph->_c0_poly._is_ntt == ciph->_c1_poly._is_ntt, "Rescale_ciph: mixed forms");
+  const bool is_ntt = ciph->_c0_poly._is_ntt;
   init_ciph(res, ciph->_c0_poly._ring_degree, level, 0,
             ciph->_scaling_factor / Get_default_sc(), ciph->_sf_degree - 1, ciph->_slots);
   int64_t*       r[2] = {res->_c0_poly._data, res->_c1_poly._data};
   const int64_t* p[2] = {ciph->_c0_poly._data, ciph->_c1_poly._data};
-  fhert_rescale_polys(c, 2, r, p, level);
+  if (is_ntt)
+    fhert_rescale_polys(c, 2, r, p, level);
+  else
+    launch_rescale_coeff(ptr2(r[0], r[1]), ptr2(p[0], p[1]), 2, (int)level);
+  res->_c0_poly._is_ntt = res->_c1_poly._is_ntt = is_ntt;
   res->_c0_poly._num_primes = res->_c1_poly._num_primes = level - 1;
   return res;
 }

@@ -306,11 +306,34 @@ moddown_rescale_kernel(u64* __restrict__ res, const u64* __restrict__ x,
   }
 }
 
+// Rescale of a polynomial in coefficient form (rns_poly.c:381-399): the dropped
+// limb is reduced as it stands (no centring, unlike the NTT-form branch),
+// res_i = (x_i - (x_last mod q_i)) * q_last^-1 mod q_i.  blockIdx.y runs over
+// the limbs of `polys` polynomials of `last` output limbs each.
+__global__ void __launch_bounds__(kThreads)
+rescale_coeff_kernel(Ptr2 res, Ptr2 x, int last, const Twiddle* __restrict__ ql_inv_row,
+                     const DevModulus* __restrict__ mods, uint32_t n) {
+  const int        g  = blockIdx.y / last, i = blockIdx.y % last;
+  const DevModulus md = mods[i];
+  const Twiddle    wi = ql_inv_row[i];
+  const u64*       xi = (g ? x.p[1] : x.p[0]) + (size_t)i * n;
+  const u64*       xl = (g ? x.p[1] : x.p[0]) + (size_t)last * n;
+  u64*             ri = (g ? res.p[1] : res.p[0]) + (size_t)i * n;
+  for (uint32_t k = blockIdx.x * kThreads + threadIdx.x; k < n; k += gridDim.x * kThreads)
+    ri[k] = mul_shoup(sub_mod(xi[k], reduce_128(0, xl[k], md), md.q), wi.w, wi.wp, md.q);
+}
+
 // ---- key inner product (rns_poly.c:516, rns_poly_impl.c:13-160) --------------
 // One reduction per output word; two coefficients per thread (16-byte loads).
 
-template <bool TWO, bool FAST>
-__global__ void __launch_bounds__(kThreads)
+// The kernel streams its operands once, so what it needs is bytes in flight:
+// the digits are taken U at a time and all operands of a group are loaded
+// before the first multiply; registers are capped for four resident CTAs per
+// SM.  EXACT: there are exactly U digits (the key switch: up to four); else
+// any number, in groups of U (a group that reaches past the last digit loads
+// nothing for the missing ones and multiplies zeros).
+template <bool TWO, bool FAST, int U, bool EXACT>
+__global__ void __launch_bounds__(kThreads, 4)
 inner_product_kernel(InnerArgs a, int num_q, const DevModulus* __restrict__ mods, uint32_t n) {
   const int        m     = blockIdx.y;  // limb among level Q limbs then K P limbs
   if ((a.skip_mask >> m) & 1) return;
@@ -331,25 +354,36 @@ inner_product_kernel(InnerArgs a, int num_q, const DevModulus* __restrict__ mods
       acc4_zero(c10);
       acc4_zero(c11);
     }
-    for (int j = 0; j < a.parts; j++) {
-      const u64* es = (j == own) ? a.in + (size_t)m * n : a.ext_ptr[j] + e_off;
-      ulonglong2 e  = reinterpret_cast<const ulonglong2*>(es)[i];
-      ulonglong2 k0 = __ldg(reinterpret_cast<const ulonglong2*>(a.key0[j] + k_off) + i);
-      if (FAST) {
-        acc4_mac(c00, e.x, k0.x);
-        acc4_mac(c01, e.y, k0.y);
-      } else {
-        mac_128(h[0], l[0], e.x, k0.x);
-        mac_128(h[1], l[1], e.y, k0.y);
+#pragma unroll 1
+    for (int base = 0; base < (EXACT ? U : a.parts); base += U) {
+      ulonglong2 e[U], k0[U], k1[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const int j = base + u;
+        if (!EXACT) e[u] = k0[u] = k1[u] = make_ulonglong2(0, 0);
+        if (EXACT || j < a.parts) {
+          const u64* es = (j == own) ? a.in + (size_t)m * n : a.ext_ptr[j] + e_off;
+          e[u]  = reinterpret_cast<const ulonglong2*>(es)[i];
+          k0[u] = __ldg(reinterpret_cast<const ulonglong2*>(a.key0[j] + k_off) + i);
+          if (TWO) k1[u] = __ldg(reinterpret_cast<const ulonglong2*>(a.key1[j] + k_off) + i);
+        }
       }
-      if (TWO) {
-        ulonglong2 k1 = __ldg(reinterpret_cast<const ulonglong2*>(a.key1[j] + k_off) + i);
+#pragma unroll
+      for (int u = 0; u < U; u++) {
         if (FAST) {
-          acc4_mac(c10, e.x, k1.x);
-          acc4_mac(c11, e.y, k1.y);
+          acc4_mac(c00, e[u].x, k0[u].x);
+          acc4_mac(c01, e[u].y, k0[u].y);
+          if (TWO) {
+            acc4_mac(c10, e[u].x, k1[u].x);
+            acc4_mac(c11, e[u].y, k1[u].y);
+          }
         } else {
-          mac_128(h[2], l[2], e.x, k1.x);
-          mac_128(h[3], l[3], e.y, k1.y);
+          mac_128(h[0], l[0], e[u].x, k0[u].x);
+          mac_128(h[1], l[1], e[u].y, k0[u].y);
+          if (TWO) {
+            mac_128(h[2], l[2], e[u].x, k1[u].x);
+            mac_128(h[3], l[3], e[u].y, k1[u].y);
+          }
         }
       }
     }
@@ -548,6 +582,16 @@ void launch_moddown_rescale(int64_t* res, const int64_t* x, const int64_t* t, in
   after_launch(c, KID_MODDOWN_COMBINE, last);
 }
 
+void launch_rescale_coeff(Ptr2 res, Ptr2 x, int polys, int level) {
+  if (level < 2) return;
+  Context*  c    = ctx();
+  const int last = level - 1;
+  prof_before(KID_RESCALE_COMBINE);
+  rescale_coeff_kernel<<<grid_for(c->N, 2, polys * last), kThreads, 0, c->stream>>>(
+      res, x, last, c->d_ql_inv + (size_t)last * c->L, c->d_mod, c->N);
+  after_launch(c, KID_RESCALE_COMBINE, polys * last);
+}
+
 void launch_inner_product(const InnerArgs& args) {
   Context* c     = ctx();
   int      limbs = args.level + c->K;
@@ -556,14 +600,23 @@ void launch_inner_product(const InnerArgs& args) {
   dim3 g    = grid_for(c->N, 4, limbs);
   bool fast = c->primes_below_2_60;
   bool two  = args.acc1 != nullptr;
-  if (two && fast)
-    inner_product_kernel<true, true><<<g, kThreads, 0, c->stream>>>(args, c->L, c->d_mod, c->N);
-  else if (two)
-    inner_product_kernel<true, false><<<g, kThreads, 0, c->stream>>>(args, c->L, c->d_mod, c->N);
-  else if (fast)
-    inner_product_kernel<false, true><<<g, kThreads, 0, c->stream>>>(args, c->L, c->d_mod, c->N);
-  else
-    inner_product_kernel<false, false><<<g, kThreads, 0, c->stream>>>(args, c->L, c->d_mod, c->N);
+#define IP_CASE(TWO_, FAST_, U_, EXACT_)                                                       \
+  inner_product_kernel<TWO_, FAST_, U_, EXACT_><<<g, kThreads, 0, c->stream>>>(args, c->L,      \
+                                                                              c->d_mod, c->N)
+#define IP_GROUPS(TWO_, FAST_)                                 \
+  do {                                                         \
+    if (args.parts == 1) IP_CASE(TWO_, FAST_, 1, true);        \
+    else if (args.parts == 2) IP_CASE(TWO_, FAST_, 2, true);   \
+    else if (args.parts == 3) IP_CASE(TWO_, FAST_, 3, true);   \
+    else if (args.parts == 4) IP_CASE(TWO_, FAST_, 4, true);   \
+    else IP_CASE(TWO_, FAST_, 2, false);                       \
+  } while (0)
+  if (two && fast) IP_GROUPS(true, true);
+  else if (two) IP_GROUPS(true, false);
+  else if (fast) IP_GROUPS(false, true);
+  else IP_GROUPS(false, false);
+#undef IP_GROUPS
+#undef IP_CASE
   after_launch(c, KID_INNER_PRODUCT, limbs);
 }
 

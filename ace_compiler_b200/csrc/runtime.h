@@ -443,6 +443,9 @@ void launch_moddown_combine(const ModDownTail& args);
 // and the second step repeats the reference's 128-bit arithmetic on the
 // (possibly slightly negative) difference exactly.
 void launch_moddown_rescale(int64_t* res, const int64_t* x, const int64_t* t, int level);
+// Rescale of `polys` polynomials in coefficient form, without centring the dropped limb
+// (rns_poly.c:381-399); res may be x
+void launch_rescale_coeff(Ptr2 res, Ptr2 x, int polys, int level);
 
 // Key inner product over `parts` digits for limbs m in [0, level+K):
 //   e_j = (in and m < level and m / alpha == j) ? in[m] : ext_ptr[j][m]

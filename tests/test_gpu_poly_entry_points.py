@@ -175,6 +175,53 @@ def test_mod_down_rescale(pair):
         gpu.free(out)
 
 
+def test_rescale_in_coefficient_form(pair):
+    """Rescale of an operand in coefficient form (rns_poly.c:381-399): the
+    dropped limb is reduced without centring and the result stays in
+    coefficient form; also in place and through Rescale_ciph."""
+    ref, gpu, rt = pair
+    n, K, rng = gpu.N, gpu.K, np.random.default_rng(37)
+    f = ref.lib.Rescale
+    f.argtypes, f.restype = [C.c_void_p, C.c_void_p], C.c_void_p
+    for level in sorted({gpu.L, 2}):
+        data = rr.uniform_limbs(rng, gpu.primes[:level], n)
+        h_in = HostPolys(rt, n, K, [data.copy()], level, is_ntt=False)
+        h_out = HostPolys(rt, n, K, [np.zeros((level, n), np.int64)], level, is_ntt=False)
+        f(C.byref(h_out.arr[0]), C.byref(h_in.arr[0]))
+        want = h_out.host(0)[: level - 1]
+        assert h_out.arr[0]._num_primes == level - 1 and not h_out.arr[0]._is_ntt
+        src = gpu.new_poly(level, data=data)
+        src.contents._is_ntt = False
+        out = gpu.new_poly(level)
+        gpu.lib.Rescale(out, src)
+        assert out.contents._num_primes == level - 1 and not out.contents._is_ntt
+        assert np.array_equal(gpu.download(out), want), level
+        gpu.lib.Rescale(src, src)          # in place
+        assert src.contents._num_primes == level - 1 and not src.contents._is_ntt
+        assert np.array_equal(gpu.download(src), want), level
+        gpu.free(src)
+        gpu.free(out)
+    level = gpu.L
+    c0 = rr.uniform_limbs(rng, gpu.primes[:level], n)
+    c1 = rr.uniform_limbs(rng, gpu.primes[:level], n)
+    wants = []
+    for d in (c0, c1):
+        h_in = HostPolys(rt, n, K, [d.copy()], level, is_ntt=False)
+        h_out = HostPolys(rt, n, K, [np.zeros((level, n), np.int64)], level, is_ntt=False)
+        f(C.byref(h_out.arr[0]), C.byref(h_in.arr[0]))
+        wants.append(h_out.host(0)[: level - 1].copy())
+    ct = gpu.new_ciph(c0, c1, sf_degree=2)
+    ct._c0_poly._is_ntt = ct._c1_poly._is_ntt = False
+    res = rt.CIPHERTEXT()
+    gpu.lib.Rescale_ciph(C.byref(res), C.byref(ct))
+    assert not res._c0_poly._is_ntt and not res._c1_poly._is_ntt
+    assert res._c0_poly._num_primes == level - 1 and res._sf_degree == 1
+    got0, got1 = gpu.ciph_to_host(res)
+    assert np.array_equal(got0, wants[0]) and np.array_equal(got1, wants[1])
+    gpu.free_ciph(ct)
+    gpu.free_ciph(res)
+
+
 def test_lpoly_interface(pair):
     """The single-limb interface of the LPOLY emit target (lpoly/poly.h:116-143)
     against the reference functions of the same names: every operation on the
