@@ -364,8 +364,10 @@ inner_product_kernel(InnerArgs a, int num_q, const DevModulus* __restrict__ mods
         if (EXACT || j < a.parts) {
           const u64* es = (j == own) ? a.in + (size_t)m * n : a.ext_ptr[j] + e_off;
           e[u]  = reinterpret_cast<const ulonglong2*>(es)[i];
-          k0[u] = __ldg(reinterpret_cast<const ulonglong2*>(a.key0[j] + k_off) + i);
-          if (TWO) k1[u] = __ldg(reinterpret_cast<const ulonglong2*>(a.key1[j] + k_off) + i);
+          // keys are read once per key switch: streamed past the L2 lines that the
+          // twiddle tables and the polynomials in flight should keep
+          k0[u] = __ldcs(reinterpret_cast<const ulonglong2*>(a.key0[j] + k_off) + i);
+          if (TWO) k1[u] = __ldcs(reinterpret_cast<const ulonglong2*>(a.key1[j] + k_off) + i);
         }
       }
 #pragma unroll
