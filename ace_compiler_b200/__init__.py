@@ -144,6 +144,8 @@ SIGNATURES = {
     "Hw_intt": (None, [I64P, I64P, C.c_size_t, C.c_uint32]),
     "Conv_poly2ntt_inplace": (POLY, [POLY]),
     "Conv_ntt2poly_inplace": (POLY, [POLY]),
+    "Conv_poly2ntt": (None, [POLY, POLY]),
+    "Conv_ntt2poly": (None, [POLY, POLY]),
     "Add_poly": (POLY, [POLY, POLY, POLY]),
     "Sub_poly": (POLY, [POLY, POLY, POLY]),
     "Mul_poly": (POLY, [POLY, POLY, POLY]),

@@ -395,6 +395,29 @@ POLY Conv_ntt2poly_inplace(POLY poly) {
   return poly;
 }
 
+// rns_poly.c:637-664: the Q limbs only; the special limbs of res are left as
+// they are, as the CPU runtime leaves them
+void Conv_poly2ntt(POLY res, POLY poly) {
+  FHERT_ASSERT(!poly->_is_ntt, "already ntt form");
+  FHERT_ASSERT(res->_ring_degree == poly->_ring_degree && res->_num_primes == poly->_num_primes &&
+                   res->_num_primes_p == poly->_num_primes_p, "size not match");
+  Context* c = ctx();
+  launch_ntt(ptr2(poly->_data), ptr2(res->_data),
+             poly_batch(c, res, poly, poly, poly->_num_primes, 0), false);
+  res->_is_ntt = true;
+}
+
+// rns_poly_impl.c:202-234: Q and special limbs
+void Conv_ntt2poly(POLY res, POLY poly) {
+  FHERT_ASSERT(poly->_is_ntt, "already coefficient form");
+  FHERT_ASSERT(res->_ring_degree == poly->_ring_degree && res->_num_primes == poly->_num_primes &&
+                   res->_num_primes_p == poly->_num_primes_p, "size not match");
+  Context* c = ctx();
+  launch_ntt(ptr2(poly->_data), ptr2(res->_data),
+             poly_batch(c, res, poly, poly, poly->_num_primes, poly->_num_primes_p), true);
+  res->_is_ntt = false;
+}
+
 static POLY binary_poly(EwOp op, POLY res, POLY a, POLY b) {
   Context* c = ctx();
   // operands in coefficient form are brought to NTT form in place, as the CPU

@@ -250,6 +250,8 @@ void Hw_intt(int64_t* res, int64_t* val, size_t mod_idx, uint32_t degree);
 
 POLY   Conv_poly2ntt_inplace(POLY poly);              /* rns_poly.c:608-699 */
 POLY   Conv_ntt2poly_inplace(POLY poly);
+void   Conv_poly2ntt(POLY res, POLY poly);               /* rns_poly.c:637: Q limbs only, as there */
+void   Conv_ntt2poly(POLY res, POLY poly);               /* rns_poly_impl.c:202 */
 POLY   Add_poly(POLY res, POLY a, POLY b);            /* rns_poly.c:852 */
 POLY   Sub_poly(POLY res, POLY a, POLY b);            /* rns_poly.c:900 */
 POLY   Mul_poly(POLY res, POLY a, POLY b);            /* rns_poly.c:950 */

@@ -222,6 +222,30 @@ def test_rescale_in_coefficient_form(pair):
     gpu.free_ciph(res)
 
 
+def test_out_of_place_conversions(pair):
+    """Conv_poly2ntt (rns_poly.c:637: transforms the Q limbs and leaves the
+    special limbs of res alone) and Conv_ntt2poly (rns_poly_impl.c:202: all
+    limbs) against the reference functions on an extended polynomial."""
+    ref, gpu, rt = pair
+    n, K, L, rng = gpu.N, gpu.K, gpu.L, np.random.default_rng(38)
+    data = rr.uniform_limbs(rng, gpu.primes, n)
+    marker = rr.uniform_limbs(rng, gpu.primes, n)       # what res holds before the call
+    for name, src_ntt in (("Conv_poly2ntt", False), ("Conv_ntt2poly", True)):
+        f = getattr(ref.lib, name)
+        f.argtypes, f.restype = [C.c_void_p, C.c_void_p], None
+        h_in = HostPolys(rt, n, K, [data.copy()], L, extended=True, is_ntt=src_ntt)
+        h_out = HostPolys(rt, n, K, [marker.copy()], L, extended=True, is_ntt=src_ntt)
+        f(C.byref(h_out.arr[0]), C.byref(h_in.arr[0]))
+        src = gpu.new_poly(L, extended=True, data=data, is_ntt=src_ntt)
+        out = gpu.new_poly(L, extended=True, data=marker, is_ntt=src_ntt)
+        getattr(gpu.lib, name)(out, src)
+        assert bool(out.contents._is_ntt) == bool(h_out.arr[0]._is_ntt) == (not src_ntt)
+        assert np.array_equal(gpu.download(out), h_out.host(0)), name
+        assert np.array_equal(gpu.download(src), data)      # the source is untouched
+        gpu.free(src)
+        gpu.free(out)
+
+
 def test_lpoly_interface(pair):
     """The single-limb interface of the LPOLY emit target (lpoly/poly.h:116-143)
     against the reference functions of the same names: every operation on the

@@ -107,6 +107,18 @@ def test_batched_conversion_round_trip(pair):
     gpu.lib.Conv_ntt2poly_inplace(p)
     assert np.array_equal(gpu.download(p), data)
     gpu.free(p)
+    # out of place (rns_poly.c:637, rns_poly_impl.c:202) and in place, many in a row
+    a = gpu.new_poly(gpu.L, data=data[: gpu.L], is_ntt=False)
+    b = gpu.new_poly(gpu.L)
+    for _ in range(6):
+        gpu.lib.Conv_poly2ntt(b, a)
+        gpu.lib.Conv_ntt2poly(a, b)
+        gpu.lib.Conv_poly2ntt_inplace(a)
+        gpu.lib.Conv_ntt2poly_inplace(a)
+    assert np.array_equal(gpu.download(a), data[: gpu.L])
+    assert np.array_equal(gpu.download(b), fwd[: gpu.L])
+    gpu.free(a)
+    gpu.free(b)
 
 
 def test_hw_vector_ops(pair):
