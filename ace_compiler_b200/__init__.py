@@ -144,6 +144,8 @@ SIGNATURES = {
     "Hw_intt": (None, [I64P, I64P, C.c_size_t, C.c_uint32]),
     "Conv_poly2ntt_inplace": (POLY, [POLY]),
     "Conv_ntt2poly_inplace": (POLY, [POLY]),
+    "Reduce_and_rescale_modup": (C.c_void_p, [POLY, POLY]),
+    "Free_precomp": (None, [C.c_void_p]),
     "Conv_poly2ntt": (None, [POLY, POLY]),
     "Conv_ntt2poly": (None, [POLY, POLY]),
     "Add_poly": (POLY, [POLY, POLY, POLY]),

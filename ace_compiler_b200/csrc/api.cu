@@ -395,15 +395,14 @@ POLY Conv_ntt2poly_inplace(POLY poly) {
   return poly;
 }
 
-// rns_poly.c:637-664: the Q limbs only; the special limbs of res are left as
-// they are, as the CPU runtime leaves them
+// rns_poly.c:637-669: Q and special limbs
 void Conv_poly2ntt(POLY res, POLY poly) {
   FHERT_ASSERT(!poly->_is_ntt, "already ntt form");
   FHERT_ASSERT(res->_ring_degree == poly->_ring_degree && res->_num_primes == poly->_num_primes &&
                    res->_num_primes_p == poly->_num_primes_p, "size not match");
   Context* c = ctx();
   launch_ntt(ptr2(poly->_data), ptr2(res->_data),
-             poly_batch(c, res, poly, poly, poly->_num_primes, 0), false);
+             poly_batch(c, res, poly, poly, poly->_num_primes, poly->_num_primes_p), false);
   res->_is_ntt = true;
 }
 
@@ -874,6 +873,68 @@ POLY Mod_down_rescale(POLY res, POLY poly) {
   res->_is_ntt     = false;
   Conv_poly2ntt_inplace(res);
   return res;
+}
+
+VALUE_LIST* Reduce_and_rescale_modup(POLY res, POLY poly) {
+  // rns_poly_impl.c:521-620
+  Context*     c     = ctx();
+  const size_t level = poly->_num_primes, n = c->N;
+  const int    K     = c->K;
+  FHERT_ASSERT(level > 1 && poly->_num_primes_p == (size_t)K,
+               "Reduce_and_rescale_modup: size not match");
+  FHERT_ASSERT(res->_data && res->_num_alloc_primes >= level,
+               "Reduce_and_rescale_modup: res must hold as many limbs as poly");
+  if (poly->_is_ntt) Conv_ntt2poly_inplace(poly);
+  // the special limbs converted to every Q prime: the CPU runtime uses res for them
+  ConvArgs args;
+  args.groups     = 1;
+  args.level      = (int)level;
+  args.out_total  = (int)level;
+  args.p_limb     = 0;
+  args.in_stride  = 1;
+  args.out_stride = K;
+  ConvGroup& cg   = args.g[0];
+  cg.in           = reinterpret_cast<const u64*>(poly->_data + p_offset(poly) * n);
+  cg.out          = reinterpret_cast<u64*>(res->_data);
+  cg.inv          = c->d_phat_inv;
+  cg.mat          = c->d_phat_mod_q;
+  cg.first_limb   = 0;
+  cg.first_prime  = c->L;
+  cg.count        = K;
+  cg.skip_start   = 0;
+  cg.skip_len     = 0;
+  launch_base_conv(args);
+  // ModDown and rescale in coefficient form, level - 1 limbs
+  const size_t out_level = level - 1;
+  int64_t*     x         = nullptr;
+  CUDA_CHECK(dev_alloc(&x, out_level * n * sizeof(int64_t), c->stream));
+  launch_moddown_rescale(x, poly->_data, res->_data, (int)level);
+  // every digit of x raised to Q_{level-1} u P, left in coefficient form
+  size_t parts = (out_level + c->alpha - 1) / c->alpha;
+  if (parts > (size_t)c->dnum) parts = (size_t)c->dnum;
+  POLY_ARR arr = Alloc_polys((uint32_t)parts, c->N, out_level, (size_t)K);
+  fhert_raise_parts(c, x, false, out_level, 0, (int)parts, arr[0]._data, out_level + K,
+                    (int)out_level);
+  for (size_t d = 0; d < parts; d++) {  // a digit's own limbs are those of x
+    size_t first = (size_t)c->alpha * d, cnt = std::min((size_t)c->alpha, out_level - first);
+    CUDA_CHECK(counted_copy(arr[d]._data + first * n, x + first * n, cnt * n * sizeof(int64_t),
+                            cudaMemcpyDeviceToDevice, c->stream));
+  }
+  CUDA_CHECK(dev_free(x, c->stream));
+  res->_num_primes = out_level;  // Modswitch(res, res)
+  VALUE_LIST* list = (VALUE_LIST*)std::calloc(1, sizeof(VALUE_LIST));
+  list->_type      = 0x4000;
+  list->_length    = parts;
+  list->_vals._p   = (void**)std::calloc(parts, sizeof(void*));
+  for (size_t d = 0; d < parts; d++) list->_vals._p[d] = &arr[d];
+  return list;
+}
+
+void Free_precomp(VALUE_LIST* precomputed) {  // rns_poly_impl.c:622-630
+  if (precomputed == nullptr) return;
+  if (precomputed->_length > 0) Free_polys((POLY_ARR)precomputed->_vals._p[0]);
+  std::free(precomputed->_vals._p);
+  std::free(precomputed);
 }
 
 void Chk_level(POLY res, POLY p0, POLY p1) {

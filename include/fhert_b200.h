@@ -250,7 +250,7 @@ void Hw_intt(int64_t* res, int64_t* val, size_t mod_idx, uint32_t degree);
 
 POLY   Conv_poly2ntt_inplace(POLY poly);              /* rns_poly.c:608-699 */
 POLY   Conv_ntt2poly_inplace(POLY poly);
-void   Conv_poly2ntt(POLY res, POLY poly);               /* rns_poly.c:637: Q limbs only, as there */
+void   Conv_poly2ntt(POLY res, POLY poly);               /* rns_poly.c:637 */
 void   Conv_ntt2poly(POLY res, POLY poly);               /* rns_poly_impl.c:202 */
 POLY   Add_poly(POLY res, POLY a, POLY b);            /* rns_poly.c:852 */
 POLY   Sub_poly(POLY res, POLY a, POLY b);            /* rns_poly.c:900 */
@@ -414,6 +414,26 @@ POLY     Init_poly_by_opnd(POLY res, POLY opnd1, POLY opnd2, bool is_ext);
 POLY     Swk_c0(POLY res, size_t size, bool is_rot, int32_t rot_idx);
 POLY     Swk_c1(POLY res, size_t size, bool is_rot, int32_t rot_idx);
 POLY_ARR Precomp(POLY_ARR res, size_t size, POLY input);   /* rns_poly.c:459 */
+
+/* ModDown, rescale and the raise of every digit of the result in one call
+ * (poly/src/rns_poly_impl.c:521-620).  poly (level Q limbs and the special
+ * limbs) is brought to coefficient form in place; res, which must hold at least
+ * level limbs, receives the base conversion of the special limbs (what the
+ * CPU runtime leaves there) and loses one level; the value is a list of
+ * ceil((level-1)/alpha) polynomials over level-1 Q limbs and the special limbs,
+ * in coefficient form, digit d raised to the whole basis.  The list has the
+ * layout of the CPU runtime's VALUE_LIST of pointers (include/util/type.h:64-80);
+ * Free_precomp releases it together with the polynomials (rns_poly_impl.c:622). */
+typedef struct VALUE_LIST {
+  int    _type;   /* 0x4000: pointers */
+  size_t _length;
+  union {
+    void**   _p;
+    int64_t* _i;
+  } _vals;
+} VALUE_LIST;
+VALUE_LIST* Reduce_and_rescale_modup(POLY res, POLY poly);
+void        Free_precomp(VALUE_LIST* precomputed);
 
 /* Single-limb polynomials of the LPOLY emit target
  * (ant/include/lpoly/poly.h:18-143, ant/lpoly/src/poly.c).  `_data` is device

@@ -222,10 +222,50 @@ def test_rescale_in_coefficient_form(pair):
     gpu.free_ciph(res)
 
 
+def test_reduce_and_rescale_modup(pair):
+    """ModDown, rescale and the raise of every digit in one call
+    (rns_poly_impl.c:521-620): the raised digits (coefficient form), what is
+    left in res, and the input left in coefficient form, against the reference."""
+    ref, gpu, rt = pair
+    n, K, rng = gpu.N, gpu.K, np.random.default_rng(39)
+
+    class HostList(C.Structure):
+        _fields_ = [("_type", C.c_int), ("_length", C.c_size_t), ("_p", C.POINTER(C.c_void_p))]
+
+    f = ref.lib.Reduce_and_rescale_modup
+    f.argtypes, f.restype = [C.c_void_p, C.c_void_p], C.POINTER(HostList)
+    gpu.lib.Reduce_and_rescale_modup.restype = C.POINTER(HostList)
+    for level in sorted({gpu.L, 2, max(2, gpu.alpha + 1)}):
+        primes = gpu.primes[:level] + gpu.primes[gpu.L:]
+        data = rr.uniform_limbs(rng, primes, n)
+        h_in = HostPolys(rt, n, K, [data.copy()], level, extended=True)
+        h_res = HostPolys(rt, n, K, [np.zeros((level, n), np.int64)], level)
+        want = f(C.byref(h_res.arr[0]), C.byref(h_in.arr[0])).contents
+        ext = gpu.new_poly(level, extended=True, data=data)
+        res = gpu.new_poly(level)
+        got = gpu.lib.Reduce_and_rescale_modup(res, ext).contents
+        assert got._type == want._type and got._length == want._length >= 1
+        for d in range(want._length):
+            hp = C.cast(want._p[d], C.POINTER(rt.POLYNOMIAL)).contents
+            gp = C.cast(got._p[d], rt.POLY)
+            words = (hp._num_primes + hp._num_primes_p) * n
+            host = np.ctypeslib.as_array(C.cast(hp._data, C.POINTER(C.c_int64)), (words,)).reshape(-1, n)
+            assert (gp.contents._num_primes, gp.contents._num_primes_p) == (hp._num_primes, hp._num_primes_p)
+            assert bool(gp.contents._is_ntt) == bool(hp._is_ntt) is False
+            assert np.array_equal(gpu.download(gp), host), (level, d)
+        assert res.contents._num_primes == h_res.arr[0]._num_primes == level - 1
+        assert np.array_equal(gpu.download(res), h_res.host(0)[: level - 1])
+        assert not ext.contents._is_ntt and not h_in.arr[0]._is_ntt
+        assert np.array_equal(gpu.download(ext), h_in.host(0))
+        gpu.lib.Free_precomp(C.cast(C.pointer(got), C.c_void_p))
+        gpu.free(ext)
+        gpu.free(res)
+
+
 def test_out_of_place_conversions(pair):
-    """Conv_poly2ntt (rns_poly.c:637: transforms the Q limbs and leaves the
-    special limbs of res alone) and Conv_ntt2poly (rns_poly_impl.c:202: all
-    limbs) against the reference functions on an extended polynomial."""
+    """Conv_poly2ntt (rns_poly.c:637) and Conv_ntt2poly (rns_poly_impl.c:202)
+    against the reference functions on an extended polynomial: Q and special
+    limbs, the source untouched."""
     ref, gpu, rt = pair
     n, K, L, rng = gpu.N, gpu.K, gpu.L, np.random.default_rng(38)
     data = rr.uniform_limbs(rng, gpu.primes, n)
