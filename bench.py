@@ -588,8 +588,24 @@ def run_resnet20(args):
     for _ in range(2):
         one_image(uncached)
     barrier()
-    lib.Fhert_pt_cache_bypass(0)
     ms_uncached = sum(a.elapsed_time(b) for a, b in uncached) / len(uncached)
+    # and the same replayed: the capture snapshots the weight messages in pinned
+    # memory, every replay copies and encodes all of them again
+    ms_uncached_replayed, uncached_state = None, ""
+    if replay:
+        lib.Fhert_replay_mode(1)
+        one_image()   # launched directly
+        one_image()   # captured
+        replayed_uncached = []
+        for _ in range(2):
+            one_image(replayed_uncached)
+        barrier()
+        if lib.Fhert_replay_state(why, len(why), C.byref(served)) == 2:
+            ms_uncached_replayed = sum(a.elapsed_time(b) for a, b in replayed_uncached) / 2
+        else:
+            uncached_state = why.value.decode()
+        lib.Fhert_replay_mode(0)
+    lib.Fhert_pt_cache_bypass(0)
 
     # per-kernel device times of one more image (outside the timed region)
     buf = C.create_string_buffer(1 << 16)
@@ -673,7 +689,12 @@ def run_resnet20(args):
                        "main_graph": main_graph_text,
                        "image_ms_launched_from_the_host": image_ms_direct,
                        "host_cpu_s_per_image_launched_from_the_host": round(direct_cpu_s, 3),
-                       "s_per_image_weights_encoded_every_image": round(ms_uncached / 1e3, 3),
+                       "s_per_image_weights_encoded_every_image": round(
+                           (ms_uncached_replayed or ms_uncached) / 1e3, 3),
+                       "s_per_image_weights_encoded_every_image_launched_from_the_host": round(
+                           ms_uncached / 1e3, 3),
+                       **({"weights_encoded_every_image_not_replayed_because": uncached_state}
+                          if uncached_state else {}),
                        "host_cpu_s_per_image": round(host_cpu_s, 3),
                        "weight_plaintexts_resident": {"entries": stats[0].value,
                                                       "GiB": round(stats[1].value / 2 ** 30, 2)},
