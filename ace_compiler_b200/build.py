@@ -7,7 +7,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libFHErt_b200.so")
 SOURCES = ["context.cu", "ntt.cu", "poly_kernels.cu", "api.cu", "rescale_static.cu", "sampling.cu",
-           "client.cu", "client_api.cu", "program_api.cu", "data_file.cu", "bootstrap.cu", "hw_queue.cu", "ciph_api.cu", "shard.cu", "encode_gpu.cu", "lpoly_api.cu"]
+           "client.cu", "client_api.cu", "program_api.cu", "data_file.cu", "bootstrap.cu", "hw_queue.cu", "ciph_api.cu", "shard.cu", "encode_gpu.cu", "lpoly_api.cu", "capture_dag.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
     "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",

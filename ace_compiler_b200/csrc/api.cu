@@ -211,7 +211,7 @@ void Alloc_poly_data(POLY poly, uint32_t degree, size_t num_q, size_t num_p) {
   poly->_is_ntt           = false;
   size_t bytes            = alloc_words(poly) * sizeof(int64_t);
   CUDA_CHECK(dev_alloc(&poly->_data, bytes, c->stream));
-  CUDA_CHECK(cudaMemsetAsync(poly->_data, 0, bytes, c->stream));
+  CUDA_CHECK(zero_async(poly->_data, bytes, c->stream));
 }
 
 void Free_poly_data(POLY poly) {
@@ -450,7 +450,7 @@ POLY Modswitch(POLY res, POLY poly) {
   if (res != poly) {
     ensure_poly(res, poly->_ring_degree, level - 1, poly->_num_primes_p);
     if (poly->_num_primes_p)  // only the Q limbs are copied: the special limbs read as zero
-      CUDA_CHECK(cudaMemsetAsync(res->_data, 0, alloc_words(res) * sizeof(int64_t), ctx()->stream));
+      CUDA_CHECK(zero_async(res->_data, alloc_words(res) * sizeof(int64_t), ctx()->stream));
     CUDA_CHECK(counted_copy(res->_data, poly->_data,
                                (level - 1) * poly->_ring_degree * sizeof(int64_t),
                                cudaMemcpyDeviceToDevice, ctx()->stream));
@@ -952,8 +952,8 @@ POLY Extend(POLY res, POLY poly) {
                "Extend: alloc_size not match");
   size_t n = c->N;
   res->_num_primes_p = c->K;
-  CUDA_CHECK(cudaMemsetAsync(res->_data + p_offset(res) * n, 0, (size_t)c->K * n * sizeof(int64_t),
-                             c->stream));
+  CUDA_CHECK(zero_async(res->_data + p_offset(res) * n, (size_t)c->K * n * sizeof(int64_t),
+                        c->stream));
   launch_mul_const(ptr2(res->_data), ptr2(poly->_data), c->d_p_mod_q,
                    poly_batch(c, res, poly, nullptr, poly->_num_primes, 0));
   res->_is_ntt = poly->_is_ntt;

@@ -961,7 +961,7 @@ void rotate_stage(Context* c, CIPHER ct, std::vector<PLAINTEXT>& plains, const F
   int64_t* c1 = ct->_c1_poly._data;
 
   // lifted = (P * c0, P * c1) on the Q limbs, zero on the special limbs
-  CUDA_CHECK(cudaMemsetAsync(lifted.p, 0, 2 * pw * sizeof(int64_t), c->stream));
+  CUDA_CHECK(zero_async(lifted.p, 2 * pw * sizeof(int64_t), c->stream));
   launch_mul_const(ptr2(lifted.p, lifted.p + pw), ptr2(c0, c1), c->d_p_mod_q, both_polys(qb));
   fhert_raise_parts(c, c1, true, level, 0, parts, digits.p, ext, (int)level);
 
@@ -1013,7 +1013,7 @@ void rotate_stage(Context* c, CIPHER ct, std::vector<PLAINTEXT>& plains, const F
     if (i == 0) {
       CUDA_CHECK(counted_copy(first.p, inner.p, pw * sizeof(int64_t), cudaMemcpyDeviceToDevice,
                                  c->stream));
-      CUDA_CHECK(cudaMemsetAsync(outer.p, 0, pw * sizeof(int64_t), c->stream));
+      CUDA_CHECK(zero_async(outer.p, pw * sizeof(int64_t), c->stream));
       CUDA_CHECK(counted_copy(outer.p + pw, inner.p + pw, pw * sizeof(int64_t),
                                  cudaMemcpyDeviceToDevice, c->stream));
       continue;

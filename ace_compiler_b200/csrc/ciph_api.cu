@@ -22,7 +22,7 @@ POLY_ARR Alloc_polys(uint32_t cnt, uint32_t degree, size_t num_q, size_t num_p) 
   size_t   words = (num_q + num_p) * (size_t)degree;
   int64_t* data  = nullptr;
   CUDA_CHECK(dev_alloc(&data, words * cnt * sizeof(int64_t), c->stream));
-  CUDA_CHECK(cudaMemsetAsync(data, 0, words * cnt * sizeof(int64_t), c->stream));
+  CUDA_CHECK(zero_async(data, words * cnt * sizeof(int64_t), c->stream));
   for (uint32_t i = 0; i < cnt; i++) {
     res[i]._ring_degree      = degree;
     res[i]._num_primes       = num_q;

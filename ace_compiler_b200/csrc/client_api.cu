@@ -223,7 +223,7 @@ void encode_scalar(Context* c, PLAIN plain, double value, uint32_t sf_degree, ui
   std::vector<int64_t> res = encode_value(c, value, level, scale, 0);
   // fill every limb with its residue: one clear, one launch for all limbs
   POLY p = &plain->_poly;
-  CUDA_CHECK(cudaMemsetAsync(p->_data, 0, (size_t)level * c->N * sizeof(int64_t), c->stream));
+  CUDA_CHECK(zero_async(p->_data, (size_t)level * c->N * sizeof(int64_t), c->stream));
   std::vector<u64> sc(res.begin(), res.end());
   launch_scalars(false, ptr2(p->_data), ptr2(p->_data), sc.data(), q_batch(level));
   p->_is_ntt = true;

@@ -590,6 +590,10 @@ void destroy_context() {
   release_prng();
   if (c->scratch) dev_free(c->scratch, c->stream);
   c->scratch = nullptr;
+  for (int64_t*& r : c->ring) {
+    if (r) dev_free(r, c->stream);
+    r = nullptr;
+  }
   dev_release_all(c->stream);
   cudaStreamSynchronize(c->stream);
   cudaFree(c->d_mod);
@@ -728,7 +732,15 @@ cudaError_t dev_alloc(void** ptr, size_t bytes, cudaStream_t stream) {
   if (bytes == 0) bytes = 256;
   bytes = (bytes + 255) & ~(size_t)255;
   if (g_private_mode) {
-    if (take_from(g_private, bytes, ptr)) return cudaSuccess;
+    // the block freed longest ago: whoever gets it waits for its former user
+    // (the dependences of a captured run go by address), so the longer ago the better
+    auto it = g_private.free_by_size.find(bytes);
+    if (it != g_private.free_by_size.end() && !it->second.empty()) {
+      *ptr = it->second.front();
+      it->second.erase(it->second.begin());
+      g_private.held -= bytes;
+      return cudaSuccess;
+    }
     cudaError_t err = cudaMalloc(ptr, bytes);
     if (err == cudaSuccess) g_private.size_of[*ptr] = bytes;
     return err;
@@ -810,6 +822,15 @@ void dev_private_to_common(cudaStream_t stream) {
 
 int64_t* scratch(size_t words) {
   Context* c = ctx();
+  if (dag_active()) {
+    const unsigned slot = c->ring_next++ % Context::kScratchRing;
+    if (c->ring_words[slot] < words) {
+      if (c->ring[slot]) CUDA_CHECK(dev_free(c->ring[slot], c->stream));
+      CUDA_CHECK(dev_alloc(&c->ring[slot], words * sizeof(int64_t), c->stream));
+      c->ring_words[slot] = words;
+    }
+    return c->ring[slot];
+  }
   if (c->scratch_words < words) {
     // the old block may still be in use by queued kernels: free it in stream order
     if (c->scratch) CUDA_CHECK(dev_free(c->scratch, c->stream));

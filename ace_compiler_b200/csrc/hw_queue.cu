@@ -226,6 +226,19 @@ struct Packer {
     if (l.chains == 0) return;
     l.first[l.chains] = (uint16_t)used;
     dim3 grid((c->N + kThreads * 2 - 1) / (kThreads * 2), l.chains);
+    DagScope dag(256);
+    if (dag.live) {
+      const size_t w = (size_t)c->N * sizeof(u64);
+      for (int k = 0; k < used; k++) {
+        const HwItem&  it   = l.item[k];
+        const uint32_t kind = it.kind & kKindMask;
+        dag.set.read(it.a, w);
+        if (kind == HW_ADD || kind == HW_SUB || kind == HW_MUL || kind == HW_MAC3) dag.set.read(it.b, w);
+        if (kind == HW_MAC3) dag.set.read(it.c, w);
+        if (!(it.kind & kNoStore)) dag.set.write(it.dst, w);
+      }
+    }
+    dag.commit();
     prof_before(KID_HW_BATCH);
     hw_batch_kernel<<<grid, kThreads, 0, c->stream>>>(l, c->d_mod, c->N);
     prof_after(KID_HW_BATCH, used);

@@ -28,6 +28,10 @@ void launch_dir(Ptr2 in, Ptr2 out, const LimbBatch& b) {
     b2.limb[i].a   = b2.limb[i].dst;
     b2.limb[i].sel = (uint8_t)((b2.limb[i].sel & 4) | ((b2.limb[i].sel >> 2) & 1));
   }
+  // both passes under one description: the second works in place on what the first wrote
+  DagScope dag(64);
+  dag.batch(b, c->N, &out, &in, nullptr);
+  dag.commit();
   const bool narrow_tiles = t.logn >= 14;
   if (!INV) {
     prof_before(KID_NTT_STRIDED);
@@ -76,6 +80,19 @@ void launch_ntt_fused(Ptr2 in, int64_t* mid, Ptr2 out, const LimbBatch& b, const
     b2.limb[i].a   = (uint16_t)i;
     b2.limb[i].sel = (uint8_t)(b.limb[i].sel & 6);
   }
+  DagScope dag(128);
+  if (dag.live) {
+    const size_t w = (size_t)c->N * sizeof(u64);
+    dag.batch(b, c->N, &out, &in, nullptr);
+    dag.set.write(mid, (size_t)b.count * w);
+    for (int i = 0; i < b.count && f.epi_kind != 0; i++) {
+      const LimbRef& lr = b.limb[i];
+      dag.set.read(f.aux.p[(lr.sel >> 1) & 1] + (size_t)lr.b * c->N, w);
+      const u64* add = f.add.p[(lr.sel >> 1) & 1];
+      if (add != nullptr) dag.set.read(add + (size_t)lr.b * c->N, w);
+    }
+  }
+  dag.commit();
   const bool narrow_tiles = t.logn >= 14;
   prof_before(KID_NTT_STRIDED);
   if (narrow_tiles) nttk::launch_strided<false, 4>(in, ptr2(mid), b1, t, c->stream, pro);

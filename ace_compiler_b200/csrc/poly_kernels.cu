@@ -434,6 +434,13 @@ void launch_elementwise(EwOp op, Ptr2 res, Ptr2 a, Ptr2 b, int64_t scalar,
                         const LimbBatch& batch) {
   if (batch.count == 0) return;
   Context* c = ctx();
+  DagScope dag(1);
+  {
+    const bool two  = op == EW_ADD || op == EW_SUB || op == EW_MUL || op == EW_MULADD;
+    const bool accu = op == EW_MULADD || op == EW_MULADD_SCALAR;
+    dag.batch(batch, c->N, &res, &a, two ? &b : nullptr, accu);
+  }
+  dag.commit();
   prof_before(KID_ELEMENTWISE);
   dim3 g = grid_for(c->N, 2, batch.count);
 #define EW_CASE(OP)                                                                        \
@@ -459,6 +466,9 @@ void launch_scalars(bool mul, Ptr2 res, Ptr2 a, const u64* per_limb, const LimbB
   Context* c = ctx();
   ScalarList sc;
   for (int i = 0; i < batch.count; i++) sc.v[i] = per_limb[i];
+  DagScope dag(2);
+  dag.batch(batch, c->N, &res, &a, nullptr);
+  dag.commit();
   prof_before(KID_ELEMENTWISE);
   dim3 g = grid_for(c->N, 2, batch.count);
   if (mul) ew_scalars_kernel<true><<<g, kThreads, 0, c->stream>>>(res, a, sc, batch, c->d_mod, c->N);
@@ -469,6 +479,9 @@ void launch_scalars(bool mul, Ptr2 res, Ptr2 a, const u64* per_limb, const LimbB
 void launch_automorphism(Ptr2 res, Ptr2 val, const uint32_t* table, const LimbBatch& batch) {
   if (batch.count == 0) return;
   Context* c = ctx();
+  DagScope dag(4);
+  dag.batch(batch, c->N, &res, &val, nullptr);
+  dag.commit();
   prof_before(KID_AUTOMORPHISM);
   automorphism_kernel<<<grid_for(c->N, 2, batch.count), kThreads, 0, c->stream>>>(
       res, val, table, batch, c->N);
@@ -479,6 +492,13 @@ void launch_automorphism_add(Ptr2 res, Ptr2 val, const int64_t* add, const uint3
                              const LimbBatch& batch) {
   if (batch.count == 0) return;
   Context* c = ctx();
+  DagScope dag(4);
+  dag.batch(batch, c->N, &res, &val, nullptr);
+  if (dag.live)
+    for (int i = 0; i < batch.count; i++)
+      if (batch.limb[i].sel & 2)
+        dag.set.read(add + (size_t)batch.limb[i].b * c->N, (size_t)c->N * sizeof(int64_t));
+  dag.commit();
   prof_before(KID_AUTOMORPHISM);
   automorphism_add_kernel<<<grid_for(c->N, 2, batch.count), kThreads, 0, c->stream>>>(
       res, val, reinterpret_cast<const u64*>(add), table, batch, c->d_mod, c->N);
@@ -488,6 +508,9 @@ void launch_automorphism_add(Ptr2 res, Ptr2 val, const int64_t* add, const uint3
 void launch_mul_const(Ptr2 res, Ptr2 val, const Twiddle* consts, const LimbBatch& batch) {
   if (batch.count == 0) return;
   Context* c = ctx();
+  DagScope dag(2);
+  dag.batch(batch, c->N, &res, &val, nullptr);
+  dag.commit();
   prof_before(KID_MUL_CONST);
   mul_const_kernel<<<grid_for(c->N, 2, batch.count), kThreads, 0, c->stream>>>(
       res, val, consts, batch, c->d_mod, c->N);
@@ -499,6 +522,13 @@ void launch_tensor_range(int64_t* d0, int64_t* d1, int64_t* d2, const int64_t* a
                          int count) {
   if (count == 0) return;
   Context* c = ctx();
+  DagScope dag(8);
+  if (dag.live) {
+    const size_t bytes = (size_t)count * c->N * sizeof(int64_t);
+    for (const int64_t* r : {a0, a1, b0, b1}) dag.set.read(r, bytes);
+    for (int64_t* w : {d0, d1, d2}) dag.set.write(w, bytes);
+  }
+  dag.commit();
   prof_before(KID_TENSOR);
   tensor_kernel<<<grid_for(c->N, 2, count), kThreads, 0, c->stream>>>(
       (u64*)d0, (u64*)d1, (u64*)d2, (const u64*)a0, (const u64*)a1, (const u64*)b0,
@@ -553,6 +583,21 @@ void launch_base_conv(const ConvArgs& args) {
   int  chunks = (max_out + kMaxOutChunk - 1) / kMaxOutChunk;
   int  chunk  = (max_out + chunks - 1) / chunks;
   dim3 grid((c->N + kThreads - 1) / kThreads, chunks, args.groups);
+  DagScope dag(16);
+  if (dag.live) {
+    const size_t w = (size_t)c->N * sizeof(u64);
+    for (int g = 0; g < args.groups; g++) {
+      const ConvGroup& cg = args.g[g];
+      dag.set.read(cg.in + (size_t)cg.first_limb * c->N, (size_t)cg.count * w);
+      for (int m = 0; m < args.out_total; m++) {
+        if (m >= cg.skip_start && m < cg.skip_start + cg.skip_len) continue;
+        if ((args.skip_mask >> m) & 1) continue;
+        int limb = m < args.level ? m : args.p_limb + (m - args.level);
+        dag.set.write(cg.out + (size_t)limb * c->N, w);
+      }
+    }
+  }
+  dag.commit();
   prof_before(KID_BASE_CONV);
   if (max_in <= 2) base_conv_dispatch<2>(c, args, grid, chunk);
   else if (max_in <= 4) base_conv_dispatch<4>(c, args, grid, chunk);
@@ -598,6 +643,28 @@ void launch_inner_product(const InnerArgs& args) {
   Context* c     = ctx();
   int      limbs = args.level + c->K;
   FHERT_ASSERT(args.parts >= 1 && args.parts <= kMaxParts, "unsupported digit count");
+  DagScope dag(32);
+  if (dag.live) {
+    const size_t n = c->N, w = n * sizeof(u64);
+    for (int m = 0; m < limbs; m++) {
+      if ((args.skip_mask >> m) & 1) continue;
+      const bool   is_q  = m < args.level;
+      const size_t e_off = (size_t)(is_q ? m : args.ext_p_limb + (m - args.level)) * n;
+      const size_t k_off = (size_t)(is_q ? m : args.key_p_limb + (m - args.level)) * n;
+      const size_t d_off = (size_t)(is_q ? m : args.acc_p_limb + (m - args.level)) * n;
+      const int    own   = (args.in != nullptr && is_q) ? m / args.alpha : -1;
+      for (int j = 0; j < args.parts; j++) {
+        dag.set.read(j == own ? args.in + (size_t)m * n : args.ext_ptr[j] + e_off, w);
+        // the "key" operands are switching keys in a key switch, but rotated
+        // ciphertext polynomials in the baby-step sums of the bootstrap
+        dag.set.read(args.key0[j] + k_off, w);
+        if (args.acc1 != nullptr) dag.set.read(args.key1[j] + k_off, w);
+      }
+      dag.set.write(args.acc0 + d_off, w);
+      if (args.acc1 != nullptr) dag.set.write(args.acc1 + d_off, w);
+    }
+  }
+  dag.commit();
   prof_before(KID_INNER_PRODUCT);
   dim3 g    = grid_for(c->N, 4, limbs);
   bool fast = c->primes_below_2_60;
@@ -625,6 +692,13 @@ void launch_inner_product(const InnerArgs& args) {
 void launch_mod_raise(int64_t* res, const int64_t* src, const LimbBatch& batch) {
   if (batch.count == 0) return;
   Context* c = ctx();
+  DagScope dag(2);
+  if (dag.live) {
+    const size_t w = (size_t)c->N * sizeof(int64_t);
+    dag.set.read(src, w);
+    for (int i = 0; i < batch.count; i++) dag.set.write(res + (size_t)batch.limb[i].dst * c->N, w);
+  }
+  dag.commit();
   prof_before(KID_MOD_RAISE);
   mod_raise_kernel<<<grid_for(c->N, 2, batch.count), kThreads, 0, c->stream>>>(
       (u64*)res, (const u64*)src, c->primes[0], batch, c->d_mod, c->N);

@@ -28,9 +28,8 @@ void init_poly_like(POLY res, POLY poly) {
     Free_poly_data(res);
     Alloc_poly_data(res, n, q, p);
   } else {
-    CUDA_CHECK(cudaMemsetAsync(res->_data, 0,
-                               res->_num_alloc_primes * (size_t)n * sizeof(int64_t),
-                               ctx()->stream));
+    CUDA_CHECK(zero_async(res->_data, res->_num_alloc_primes * (size_t)n * sizeof(int64_t),
+                          ctx()->stream));
     res->_ring_degree  = n;
     res->_num_primes   = q;
     res->_num_primes_p = p;
@@ -128,6 +127,7 @@ struct ImageReplay {
   cudaGraphExec_t         exec        = nullptr;
   uint64_t                launches    = 0;  // launches of this library one replay stands for
   uint64_t                replays     = 0;
+  uint64_t                dag_nodes = 0, dag_edges = 0, dag_barriers = 0;  // of the captured graph
   std::vector<PinnedCiph> inputs, outputs;
   std::string             why_off;
   // pinned snapshots of the host data the captured run copies to the device
@@ -221,6 +221,7 @@ const void* image_capture_stage(const void* src, size_t bytes) {
 
 void image_capture_break(const char* why) {
   if (!g_replay.capturing) return;
+  dag_end(nullptr, nullptr, nullptr);
   g_replay.capturing = false;  // first: the calls below pass the same guards
   Context*    c     = ctx_noflush();
   cudaGraph_t graph = nullptr;
@@ -660,16 +661,26 @@ static void capture_run() {
   const uint64_t launches0 = c->launches;
   CUDA_CHECK(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeRelaxed));
   g_replay.capturing = true;
+  dag_begin();
   bool ok = Main_graph();
   c       = ctx();  // work still deferred belongs to this run
   c->raised.valid = false;
   if (g_replay.capturing) {
+    dag_end(&g_replay.dag_nodes, &g_replay.dag_edges, &g_replay.dag_barriers);
     g_replay.capturing = false;
     cudaGraph_t graph  = nullptr;
     CUDA_CHECK(cudaStreamEndCapture(c->stream, &graph));
     FHERT_ASSERT(graph != nullptr, "Run_main_graph: the capture of the program run was lost");
     launch_captured(c, graph, true);
     g_replay.launches = c->launches - launches0;
+    if (const char* e = std::getenv("FHERT_REPLAY_STATS"))
+      if (e[0] == '1')
+        std::fprintf(stderr, "[FHERT_REPLAY] %llu launches captured; %llu described nodes, %llu "
+                     "dependences among them, %llu barriers, %llu joins\n",
+                     (unsigned long long)g_replay.launches, (unsigned long long)g_replay.dag_nodes,
+                     (unsigned long long)g_replay.dag_edges,
+                     (unsigned long long)(g_replay.dag_barriers & 0xffffffffu),
+                     (unsigned long long)(g_replay.dag_barriers >> 32));
     for (auto& kv : g_io.outputs)
       for (size_t i = 0; i < kv.second.size(); i++)
         if (kv.second[i] != nullptr) g_replay.outputs.push_back(PinnedCiph{kv.first, i, *kv.second[i]});

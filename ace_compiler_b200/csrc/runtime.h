@@ -172,6 +172,12 @@ struct Context {
   // scratch polynomial storage reused by the fused operations
   int64_t* scratch      = nullptr;
   size_t   scratch_words = 0;
+  // scratch blocks of a captured run, used in turn: with one block every call
+  // that needs scratch would have to wait for the one before it
+  static constexpr int kScratchRing = 8;
+  int64_t* ring[kScratchRing]       = {};
+  size_t   ring_words[kScratchRing] = {};
+  unsigned ring_next                = 0;
 };
 
 // Optional per-kernel timing: when enabled every launch is bracketed by CUDA
@@ -256,6 +262,60 @@ void dev_release_all(cudaStream_t stream);  // gives every kept block back to th
 void dev_private_mode(bool on);
 bool dev_take_private(void* ptr);            // takes one given block out of the private lists
 void dev_private_to_common(cudaStream_t s);  // ends the separation: every private block joins the common lists
+
+// ---- capture_dag.cu: data-flow dependences of a captured program run ----
+// What one launch (or one group of launches that run one after the other)
+// reads and writes, as byte ranges; adjacent ranges are merged.
+struct AccessSet {
+  std::vector<std::pair<uintptr_t, uintptr_t>> reads, writes;
+  static void add(std::vector<std::pair<uintptr_t, uintptr_t>>& v, const void* p, size_t bytes) {
+    if (p == nullptr || bytes == 0) return;
+    uintptr_t a = (uintptr_t)p, b = a + bytes;
+    if (!v.empty() && v.back().second == a) v.back().second = b;
+    else v.emplace_back(a, b);
+  }
+  void read(const void* p, size_t bytes) { add(reads, p, bytes); }
+  void write(const void* p, size_t bytes) { add(writes, p, bytes); }
+};
+void dag_begin();  // at the start of a capture
+void dag_end(uint64_t* nodes, uint64_t* edges, uint64_t* barriers);
+bool dag_active();
+bool dag_family_on(int family);  // debugging aid: FHERT_DAG_SKIP masks families out
+void dag_before(const AccessSet& a);  // sets the dependences of what is launched next
+void dag_after();                     // takes note of the node(s) just captured
+// Around a launch: fill `set` when `live`, commit(), launch; the destructor
+// records the new node.  Launches without such a scope are ordered after all
+// earlier and before all later ones.
+struct DagScope {
+  AccessSet set;
+  bool      live;
+  explicit DagScope(int family = 0) : live(dag_active() && dag_family_on(family)) {}
+  void commit() { if (live) dag_before(set); }
+  ~DagScope() { if (live) dag_after(); }
+  // limbs of a batch: sel bit 0 picks the base of operand a, bit 1 of b, bit 2 of the result
+  void batch(const LimbBatch& b, uint32_t n, const Ptr2* res, const Ptr2* a, const Ptr2* bb,
+             bool res_is_read = false) {
+    if (!live) return;
+    const size_t w = (size_t)n * sizeof(u64);
+    for (int i = 0; i < b.count; i++) {
+      const LimbRef& lr = b.limb[i];
+      if (a) set.read(a->p[lr.sel & 1] + (size_t)lr.a * n, w);
+      if (bb) set.read(bb->p[(lr.sel >> 1) & 1] + (size_t)lr.b * n, w);
+      if (res) {
+        const u64* r = res->p[(lr.sel >> 2) & 1] + (size_t)lr.dst * n;
+        set.write(r, w);
+        if (res_is_read) set.read(r, w);
+      }
+    }
+  }
+};
+// cudaMemsetAsync of device memory to zero on the library stream, described
+inline cudaError_t zero_async(void* p, size_t bytes, cudaStream_t stream) {
+  DagScope dag(512);
+  if (dag.live) dag.set.write(p, bytes);
+  dag.commit();
+  return cudaMemsetAsync(p, 0, bytes, stream);
+}
 
 // ---- program_api.cu: a captured program run ----
 // True while Run_main_graph is capturing the launches of a program run.
@@ -488,6 +548,12 @@ inline cudaError_t counted_copy(void* dst, const void* src, size_t bytes, cudaMe
     if (kind == cudaMemcpyHostToDevice) c->h2d_bytes += bytes;
     else if (kind == cudaMemcpyDeviceToHost) c->d2h_bytes += bytes;
   }
+  DagScope dag(1024);
+  if (dag.live) {
+    if (kind == cudaMemcpyDeviceToDevice) dag.set.read(src, bytes);
+    dag.set.write(dst, bytes);
+  }
+  dag.commit();
   return cudaMemcpyAsync(dst, src, bytes, kind, stream);
 }
 }  // namespace fhert
