@@ -271,6 +271,7 @@ SIGNATURES = {
     "Fhert_pt_cache_bypass": (None, [C.c_int]),
     "Fhert_replay_mode": (None, [C.c_int]),
     "Fhert_replay_state": (C.c_int, [C.c_char_p, C.c_size_t, C.POINTER(C.c_uint64)]),
+    "Fhert_replay_graph": (None, [C.POINTER(C.c_uint64)] * 5),
     "Validate_impl": (None, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.c_uint32, C.c_int32]),
     "Validate_value_range": (None, [C.c_bool]),
     "Within_value_range": (C.c_bool, [CIPHER, C.POINTER(C.c_double), C.c_uint32]),

@@ -110,7 +110,8 @@ void dag_begin() {
   g_dag.on = !off;
 }
 
-void dag_end(uint64_t* nodes, uint64_t* edges, uint64_t* barriers) {
+void dag_end(uint64_t* nodes, uint64_t* edges, uint64_t* barriers, uint64_t* longest_chain) {
+  if (longest_chain) *longest_chain = g_dag.max_depth;
   if (nodes) *nodes = g_dag.nodes;
   if (edges) *edges = g_dag.edges;
   if (barriers) *barriers = g_dag.barriers + (g_dag.joins << 32);

@@ -226,7 +226,7 @@ struct Packer {
     if (l.chains == 0) return;
     l.first[l.chains] = (uint16_t)used;
     dim3 grid((c->N + kThreads * 2 - 1) / (kThreads * 2), l.chains);
-    DagScope dag(256);
+    DagScope dag(DAG_RECORDED_BATCH);
     if (dag.live) {
       const size_t w = (size_t)c->N * sizeof(u64);
       for (int k = 0; k < used; k++) {

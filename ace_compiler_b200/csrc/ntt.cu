@@ -29,7 +29,7 @@ void launch_dir(Ptr2 in, Ptr2 out, const LimbBatch& b) {
     b2.limb[i].sel = (uint8_t)((b2.limb[i].sel & 4) | ((b2.limb[i].sel >> 2) & 1));
   }
   // both passes under one description: the second works in place on what the first wrote
-  DagScope dag(64);
+  DagScope dag(DAG_NTT);
   dag.batch(b, c->N, &out, &in, nullptr);
   dag.commit();
   const bool narrow_tiles = t.logn >= 14;
@@ -80,7 +80,7 @@ void launch_ntt_fused(Ptr2 in, int64_t* mid, Ptr2 out, const LimbBatch& b, const
     b2.limb[i].a   = (uint16_t)i;
     b2.limb[i].sel = (uint8_t)(b.limb[i].sel & 6);
   }
-  DagScope dag(128);
+  DagScope dag(DAG_NTT_FUSED);
   if (dag.live) {
     const size_t w = (size_t)c->N * sizeof(u64);
     dag.batch(b, c->N, &out, &in, nullptr);

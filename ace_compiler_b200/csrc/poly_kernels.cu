@@ -434,7 +434,7 @@ void launch_elementwise(EwOp op, Ptr2 res, Ptr2 a, Ptr2 b, int64_t scalar,
                         const LimbBatch& batch) {
   if (batch.count == 0) return;
   Context* c = ctx();
-  DagScope dag(1);
+  DagScope dag(DAG_ELEMENTWISE);
   {
     const bool two  = op == EW_ADD || op == EW_SUB || op == EW_MUL || op == EW_MULADD;
     const bool accu = op == EW_MULADD || op == EW_MULADD_SCALAR;
@@ -466,7 +466,7 @@ void launch_scalars(bool mul, Ptr2 res, Ptr2 a, const u64* per_limb, const LimbB
   Context* c = ctx();
   ScalarList sc;
   for (int i = 0; i < batch.count; i++) sc.v[i] = per_limb[i];
-  DagScope dag(2);
+  DagScope dag(DAG_PER_LIMB_CONST);
   dag.batch(batch, c->N, &res, &a, nullptr);
   dag.commit();
   prof_before(KID_ELEMENTWISE);
@@ -479,7 +479,7 @@ void launch_scalars(bool mul, Ptr2 res, Ptr2 a, const u64* per_limb, const LimbB
 void launch_automorphism(Ptr2 res, Ptr2 val, const uint32_t* table, const LimbBatch& batch) {
   if (batch.count == 0) return;
   Context* c = ctx();
-  DagScope dag(4);
+  DagScope dag(DAG_AUTOMORPHISM);
   dag.batch(batch, c->N, &res, &val, nullptr);
   dag.commit();
   prof_before(KID_AUTOMORPHISM);
@@ -492,7 +492,7 @@ void launch_automorphism_add(Ptr2 res, Ptr2 val, const int64_t* add, const uint3
                              const LimbBatch& batch) {
   if (batch.count == 0) return;
   Context* c = ctx();
-  DagScope dag(4);
+  DagScope dag(DAG_AUTOMORPHISM);
   dag.batch(batch, c->N, &res, &val, nullptr);
   if (dag.live)
     for (int i = 0; i < batch.count; i++)
@@ -508,7 +508,7 @@ void launch_automorphism_add(Ptr2 res, Ptr2 val, const int64_t* add, const uint3
 void launch_mul_const(Ptr2 res, Ptr2 val, const Twiddle* consts, const LimbBatch& batch) {
   if (batch.count == 0) return;
   Context* c = ctx();
-  DagScope dag(2);
+  DagScope dag(DAG_PER_LIMB_CONST);
   dag.batch(batch, c->N, &res, &val, nullptr);
   dag.commit();
   prof_before(KID_MUL_CONST);
@@ -522,7 +522,7 @@ void launch_tensor_range(int64_t* d0, int64_t* d1, int64_t* d2, const int64_t* a
                          int count) {
   if (count == 0) return;
   Context* c = ctx();
-  DagScope dag(8);
+  DagScope dag(DAG_TENSOR);
   if (dag.live) {
     const size_t bytes = (size_t)count * c->N * sizeof(int64_t);
     for (const int64_t* r : {a0, a1, b0, b1}) dag.set.read(r, bytes);
@@ -583,7 +583,7 @@ void launch_base_conv(const ConvArgs& args) {
   int  chunks = (max_out + kMaxOutChunk - 1) / kMaxOutChunk;
   int  chunk  = (max_out + chunks - 1) / chunks;
   dim3 grid((c->N + kThreads - 1) / kThreads, chunks, args.groups);
-  DagScope dag(16);
+  DagScope dag(DAG_BASE_CONV);
   if (dag.live) {
     const size_t w = (size_t)c->N * sizeof(u64);
     for (int g = 0; g < args.groups; g++) {
@@ -643,7 +643,7 @@ void launch_inner_product(const InnerArgs& args) {
   Context* c     = ctx();
   int      limbs = args.level + c->K;
   FHERT_ASSERT(args.parts >= 1 && args.parts <= kMaxParts, "unsupported digit count");
-  DagScope dag(32);
+  DagScope dag(DAG_INNER_PRODUCT);
   if (dag.live) {
     const size_t n = c->N, w = n * sizeof(u64);
     for (int m = 0; m < limbs; m++) {
@@ -692,7 +692,7 @@ void launch_inner_product(const InnerArgs& args) {
 void launch_mod_raise(int64_t* res, const int64_t* src, const LimbBatch& batch) {
   if (batch.count == 0) return;
   Context* c = ctx();
-  DagScope dag(2);
+  DagScope dag(DAG_PER_LIMB_CONST);
   if (dag.live) {
     const size_t w = (size_t)c->N * sizeof(int64_t);
     dag.set.read(src, w);

@@ -127,7 +127,7 @@ struct ImageReplay {
   cudaGraphExec_t         exec        = nullptr;
   uint64_t                launches    = 0;  // launches of this library one replay stands for
   uint64_t                replays     = 0;
-  uint64_t                dag_nodes = 0, dag_edges = 0, dag_barriers = 0;  // of the captured graph
+  uint64_t                dag_nodes = 0, dag_edges = 0, dag_barriers = 0, dag_chain = 0;  // of the captured graph
   std::vector<PinnedCiph> inputs, outputs;
   std::string             why_off;
   // pinned snapshots of the host data the captured run copies to the device
@@ -666,7 +666,7 @@ static void capture_run() {
   c       = ctx();  // work still deferred belongs to this run
   c->raised.valid = false;
   if (g_replay.capturing) {
-    dag_end(&g_replay.dag_nodes, &g_replay.dag_edges, &g_replay.dag_barriers);
+    dag_end(&g_replay.dag_nodes, &g_replay.dag_edges, &g_replay.dag_barriers, &g_replay.dag_chain);
     g_replay.capturing = false;
     cudaGraph_t graph  = nullptr;
     CUDA_CHECK(cudaStreamEndCapture(c->stream, &graph));
@@ -724,6 +724,20 @@ void Fhert_replay_mode(int on) {
   } else {
     g_replay.mode = 0;
   }
+}
+
+// Shape of the captured graph: launches of this library in it, launches (or
+// groups of launches) whose memory accesses were described, dependences among
+// those, launches nobody described (each orders everything around it), and the
+// longest chain of described launches.  Zeros when nothing is captured.
+void Fhert_replay_graph(uint64_t* launches, uint64_t* described, uint64_t* dependences,
+                        uint64_t* undescribed_barriers, uint64_t* longest_chain) {
+  const bool have = g_replay.exec != nullptr;
+  if (launches) *launches = have ? g_replay.launches : 0;
+  if (described) *described = have ? g_replay.dag_nodes : 0;
+  if (dependences) *dependences = have ? g_replay.dag_edges : 0;
+  if (undescribed_barriers) *undescribed_barriers = have ? (g_replay.dag_barriers & 0xffffffffu) : 0;
+  if (longest_chain) *longest_chain = have ? g_replay.dag_chain : 0;
 }
 
 // 0: off (why, when given, receives the reason the mode went off by itself),

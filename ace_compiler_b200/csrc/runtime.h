@@ -278,9 +278,17 @@ struct AccessSet {
   void write(const void* p, size_t bytes) { add(writes, p, bytes); }
 };
 void dag_begin();  // at the start of a capture
-void dag_end(uint64_t* nodes, uint64_t* edges, uint64_t* barriers);
+void dag_end(uint64_t* nodes, uint64_t* edges, uint64_t* barriers, uint64_t* longest_chain = nullptr);
 bool dag_active();
-bool dag_family_on(int family);  // debugging aid: FHERT_DAG_SKIP masks families out
+// Families of described launches.  Debugging aid: FHERT_DAG_SKIP=<sum of families>
+// leaves those launches undescribed (they then order everything around them),
+// which tells which description is at fault when a replay differs from a direct run.
+enum DagFamily {
+  DAG_ELEMENTWISE = 1, DAG_PER_LIMB_CONST = 2, DAG_AUTOMORPHISM = 4, DAG_TENSOR = 8,
+  DAG_BASE_CONV = 16, DAG_INNER_PRODUCT = 32, DAG_NTT = 64, DAG_NTT_FUSED = 128,
+  DAG_RECORDED_BATCH = 256, DAG_CLEAR = 512, DAG_COPY = 1024
+};
+bool dag_family_on(int family);
 void dag_before(const AccessSet& a);  // sets the dependences of what is launched next
 void dag_after();                     // takes note of the node(s) just captured
 // Around a launch: fill `set` when `live`, commit(), launch; the destructor
@@ -311,7 +319,7 @@ struct DagScope {
 };
 // cudaMemsetAsync of device memory to zero on the library stream, described
 inline cudaError_t zero_async(void* p, size_t bytes, cudaStream_t stream) {
-  DagScope dag(512);
+  DagScope dag(DAG_CLEAR);
   if (dag.live) dag.set.write(p, bytes);
   dag.commit();
   return cudaMemsetAsync(p, 0, bytes, stream);
@@ -548,7 +556,7 @@ inline cudaError_t counted_copy(void* dst, const void* src, size_t bytes, cudaMe
     if (kind == cudaMemcpyHostToDevice) c->h2d_bytes += bytes;
     else if (kind == cudaMemcpyDeviceToHost) c->d2h_bytes += bytes;
   }
-  DagScope dag(1024);
+  DagScope dag(DAG_COPY);
   if (dag.live) {
     if (kind == cudaMemcpyDeviceToDevice) dag.set.read(src, bytes);
     dag.set.write(dst, bytes);

@@ -501,8 +501,15 @@ def run_resnet20(args):
     stream = torch.cuda.ExternalStream(lib.Fhert_stream(), device=torch.device("cuda", local))
     rng = np.random.default_rng(2000 + rank)
 
-    def one_image(events=None):
-        vals = np.ascontiguousarray(rng.uniform(-1.0, 1.0, 3 * 32 * 32))
+    pin_words = (C.c_uint32 * 16)(*[(7 * 2654435761 + 40503 * k) & 0xffffffff for k in range(16)])
+    pin_vals = np.ascontiguousarray(np.random.default_rng(99).uniform(-1.0, 1.0, 3 * 32 * 32))
+
+    def one_image(events=None, pinned=False):
+        if pinned:  # the same input under the same encryption randomness: results must repeat bit for bit
+            lib.Fhert_seed(pin_words, 0, 1700000000000007 + rank)
+            vals = pin_vals
+        else:
+            vals = np.ascontiguousarray(rng.uniform(-1.0, 1.0, 3 * 32 * 32))
         t = lib.Alloc_tensor(1, 3, 32, 32, vals.ctypes.data_as(C.POINTER(C.c_double)))
         lib.Prepare_input(t, b"input")
         lib.Free_tensor(t)
@@ -535,8 +542,21 @@ def run_resnet20(args):
     replay = not args.no_replay
     if replay:
         lib.Fhert_replay_mode(1)
-    for _ in range(max(3 if replay else 1, args.warmup)):
+    # the first (directly launched) and the last warm-up image (a replay) are the same
+    # pinned image: the replayed graph has to reproduce the direct launches bit for bit
+    warm = max(3 if replay else 1, args.warmup)
+    first_logits = one_image(pinned=True)
+    for _ in range(warm - 2):
         one_image()
+    replay_checked = None
+    if warm >= 2:
+        again = one_image(pinned=True)
+        if replay and lib.Fhert_replay_state(None, 0, None) == 2:
+            replay_checked = again == first_logits
+            if not replay_checked:  # never report numbers of a graph that computes something else
+                print("replayed run differs from the direct run: replay switched off", file=sys.stderr)
+                lib.Fhert_replay_mode(0)
+                replay = False
     barrier()
     launches0, (h2d0, d2h0) = lib.Fhert_kernel_launches(), transfer()
     events = []
@@ -563,12 +583,20 @@ def run_resnet20(args):
     # kernel from the host (outside the timed region)
     why, served = C.create_string_buffer(256), C.c_uint64()
     replay_state = lib.Fhert_replay_state(why, len(why), C.byref(served))
+    graph_shape = None
     if replay_state == 2:
+        g5 = [C.c_uint64() for _ in range(5)]
+        lib.Fhert_replay_graph(*[C.byref(x) for x in g5])
+        graph_shape = dict(zip(("launches", "described_launch_groups", "dependences",
+                                "undescribed_barriers", "longest_chain"), (x.value for x in g5)))
         main_graph_text = (f"captured once as one CUDA graph of {launches // args.steps} kernel launches "
                            f"(second warm-up image), replayed for every timed image "
                            f"({served.value} replays so far); the input ciphertext is new every image")
     elif replay:
         main_graph_text = "launched kernel by kernel from the host; replay went off: " + why.value.decode()
+    elif replay_checked is False:
+        main_graph_text = ("launched kernel by kernel from the host: the replayed run differed from the "
+                           "direct run of the same pinned image, replay was switched off")
     else:
         main_graph_text = "launched kernel by kernel from the host (--no-replay)"
     lib.Fhert_replay_mode(0)
@@ -687,6 +715,8 @@ def run_resnet20(args):
                        "setup_s": round(setup_s, 1),
                        "image_ms_this_rank": image_ms,
                        "main_graph": main_graph_text,
+                       "replay_equals_direct_launch_on_a_pinned_image": replay_checked,
+                       "captured_graph": graph_shape,
                        "image_ms_launched_from_the_host": image_ms_direct,
                        "host_cpu_s_per_image_launched_from_the_host": round(direct_cpu_s, 3),
                        "s_per_image_weights_encoded_every_image": round(

@@ -589,6 +589,14 @@ void Fhert_replay_mode(int on);
 /* 0 off (why receives the reason when the mode went off by itself), 1 on and
  * nothing captured yet, 2 replaying; replays = runs served by the graph */
 int  Fhert_replay_state(char* why, size_t cap, uint64_t* replays);
+/* Shape of the captured graph.  The graph is not the chain of launches in
+ * stream order: while a run is captured every launch says which memory it
+ * reads and writes, and depends on exactly the launches that last wrote what it
+ * reads and last wrote or read what it writes, so independent branches of the
+ * program run side by side (FHERT_REPLAY_DAG=0 keeps stream order).  A launch
+ * nobody described orders everything before it before everything after it. */
+void Fhert_replay_graph(uint64_t* launches, uint64_t* described, uint64_t* dependences,
+                        uint64_t* undescribed_barriers, uint64_t* longest_chain);
 
 /* Weight data file named by Get_rt_data_info (message files of floats,
  * fhe-cmplr/include/fhe/core/rt_data_def.h:91-112; opened by Prepare_context)
