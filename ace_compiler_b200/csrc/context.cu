@@ -733,16 +733,32 @@ cudaError_t dev_alloc(void** ptr, size_t bytes, cudaStream_t stream) {
   bytes = (bytes + 255) & ~(size_t)255;
   if (g_private_mode) {
     // the block freed longest ago: whoever gets it waits for its former user
-    // (the dependences of a captured run go by address), so the longer ago the better
-    auto it = g_private.free_by_size.find(bytes);
-    if (it != g_private.free_by_size.end() && !it->second.empty()) {
+    // (the dependences of a captured run go by address), so the longer ago the
+    // better; and during a capture only when a few younger ones are waiting behind
+    // it: a size class with a single block would chain every user of that size to
+    // the one before (FHERT_REPLAY_DEPTH, default 8; ResNet-20: 1010 / 945 / 920 ms
+    // per image with 0 / 3 / 8)
+    static const size_t depth = [] {
+      const char* e = std::getenv("FHERT_REPLAY_DEPTH");
+      return e != nullptr ? (size_t)std::strtoul(e, nullptr, 10) : (size_t)8;
+    }();
+    auto it       = g_private.free_by_size.find(bytes);
+    size_t  have  = it != g_private.free_by_size.end() ? it->second.size() : 0;
+    cudaError_t err = cudaErrorMemoryAllocation;
+    if (have <= (image_capturing() ? depth : 0)) {
+      err = cudaMalloc(ptr, bytes);
+      if (err == cudaSuccess) {
+        g_private.size_of[*ptr] = bytes;
+        return err;
+      }
+      cudaGetLastError();  // out of memory: fall back to the oldest free block, if any
+    }
+    if (have > 0) {
       *ptr = it->second.front();
       it->second.erase(it->second.begin());
       g_private.held -= bytes;
       return cudaSuccess;
     }
-    cudaError_t err = cudaMalloc(ptr, bytes);
-    if (err == cudaSuccess) g_private.size_of[*ptr] = bytes;
     return err;
   }
   if (take_from(g_pool, bytes, ptr)) return cudaSuccess;

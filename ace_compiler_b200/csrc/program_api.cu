@@ -637,6 +637,17 @@ static void capture_run() {
     c->scratch       = nullptr;
     c->scratch_words = 0;
   }
+  // idle blocks of the common lists go back to the driver: the capture needs the room
+  dev_release_all(c->stream);
+  CUDA_CHECK(cudaStreamSynchronize(c->stream));
+  {
+    int           dev  = 0;
+    cudaMemPool_t pool = nullptr;
+    CUDA_CHECK(cudaGetDevice(&dev));
+    if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess && pool != nullptr)
+      cudaMemPoolTrimTo(pool, 0);
+    cudaGetLastError();
+  }
   dev_private_mode(true);
   g_replay.inputs.clear();
   g_replay.outputs.clear();
