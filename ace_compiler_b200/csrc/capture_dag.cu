@@ -27,21 +27,16 @@
 #include <unordered_map>
 #include <vector>
 
+#include "access_map.h"
 #include "runtime.h"
 
 namespace fhert {
 
 namespace {
 
-struct Seg {
-  uintptr_t                    end;
-  cudaGraphNode_t              writer;  // nullptr: not written since the last barrier
-  std::vector<cudaGraphNode_t> readers;
-};
-
 struct DagState {
   bool                           on = false;
-  std::map<uintptr_t, Seg>       segs;     // disjoint [start, end) pieces of touched memory
+  AccessMap<cudaGraphNode_t>     map;      // who wrote and read what since the last barrier
   std::vector<cudaGraphNode_t>   leaves;   // nodes nothing depends on yet (sorted)
   std::vector<cudaGraphNode_t>   barrier;  // every new node depends on these
   std::vector<cudaGraphNode_t>   deps;     // of the launch being described (sorted, unique)
@@ -62,25 +57,6 @@ constexpr size_t kMaxLeaves = 48;
 void sort_unique(std::vector<cudaGraphNode_t>& v) {
   std::sort(v.begin(), v.end());
   v.erase(std::unique(v.begin(), v.end()), v.end());
-}
-
-// makes `at` a segment boundary if it falls inside a segment
-void split_at(uintptr_t at) {
-  auto it = g_dag.segs.upper_bound(at);
-  if (it == g_dag.segs.begin()) return;
-  --it;
-  if (it->first < at && at < it->second.end) {
-    Seg right        = it->second;
-    it->second.end   = at;
-    g_dag.segs[at]   = right;
-  }
-}
-
-template <typename F>
-void for_each_seg(uintptr_t a, uintptr_t b, F&& f) {
-  split_at(a);
-  split_at(b);
-  for (auto it = g_dag.segs.lower_bound(a); it != g_dag.segs.end() && it->first < b; ++it) f(it->second);
 }
 
 std::vector<cudaGraphNode_t> stream_deps(cudaStream_t stream) {
@@ -139,19 +115,11 @@ void dag_before(const AccessSet& a) {
     // went before (they depended on every leaf) and before all that follows
     g_dag.barrier = cur;
     g_dag.leaves  = cur;
-    g_dag.segs.clear();
+    g_dag.map.clear();
     g_dag.barriers++;
   }
   g_dag.deps = g_dag.barrier;
-  for (const auto& r : a.reads)
-    for_each_seg(r.first, r.second, [&](Seg& s) {
-      if (s.writer) g_dag.deps.push_back(s.writer);
-    });
-  for (const auto& w : a.writes)
-    for_each_seg(w.first, w.second, [&](Seg& s) {
-      if (s.writer) g_dag.deps.push_back(s.writer);
-      g_dag.deps.insert(g_dag.deps.end(), s.readers.begin(), s.readers.end());
-    });
+  g_dag.map.dependences(a.reads, a.writes, g_dag.deps);
   sort_unique(g_dag.deps);
   g_dag.max_deps = std::max(g_dag.max_deps, g_dag.deps.size());
   set_stream_deps(stream, g_dag.deps);
@@ -186,30 +154,7 @@ void dag_after() {
   }
   g_dag.nodes++;
   g_dag.edges += g_dag.deps.size();
-  // memory map: written pieces have one writer and no readers, read pieces one more reader
-  for (const auto& w : a.writes) {
-    split_at(w.first);
-    split_at(w.second);
-    auto lo = g_dag.segs.lower_bound(w.first), hi = g_dag.segs.lower_bound(w.second);
-    g_dag.segs.erase(lo, hi);
-    g_dag.segs[w.first] = Seg{w.second, node, {}};
-  }
-  for (const auto& r : a.reads) {
-    // pieces of the range never touched before get a segment without writer
-    uintptr_t at = r.first;
-    split_at(r.first);
-    split_at(r.second);
-    std::vector<std::pair<uintptr_t, uintptr_t>> gaps;
-    for (auto it = g_dag.segs.lower_bound(r.first); it != g_dag.segs.end() && it->first < r.second; ++it) {
-      if (it->first > at) gaps.emplace_back(at, it->first);
-      at = it->second.end;
-    }
-    if (at < r.second) gaps.emplace_back(at, r.second);
-    for (auto& g : gaps) g_dag.segs[g.first] = Seg{g.second, nullptr, {}};
-    for_each_seg(r.first, r.second, [&](Seg& s) {
-      if (s.writer != node) s.readers.push_back(node);
-    });
-  }
+  g_dag.map.record(a.reads, a.writes, node);
   // leaves: the new node replaces the ones it depends on
   std::vector<cudaGraphNode_t> next;
   std::set_difference(g_dag.leaves.begin(), g_dag.leaves.end(), g_dag.deps.begin(), g_dag.deps.end(),
