@@ -759,7 +759,10 @@ cudaError_t dev_alloc(void** ptr, size_t bytes, cudaStream_t stream) {
       g_private.held -= bytes;
       return cudaSuccess;
     }
-    return err;
+    if (!image_capturing()) return err;
+    // no room for the captured run's own blocks: what was captured so far is
+    // launched, the rest of the run is launched directly from the common lists
+    image_capture_break("out of device memory for the blocks of the captured run");
   }
   if (take_from(g_pool, bytes, ptr)) return cudaSuccess;
   cudaError_t err = cudaMallocAsync(ptr, bytes, stream);
